@@ -1,0 +1,102 @@
+/* C ABI of libtrainkernel_rt.so: load and launch one generated training-step kernel.
+ *
+ * This is the native boundary of the compiled-step path.  In the reference the
+ * same boundary is a pybind11 module that is generated and compiled together
+ * with every kernel and exposes `launch(inputs, outputs, workspace)` and
+ * `resource_usage()` (reference: trainkernel/codegen.py:862-896, called from
+ * trainkernel/runtime.py:39-43 and :96).  Here it is one prebuilt shared library
+ * over the CUDA driver API with plain pointers and sizes in every signature; it
+ * has no PyTorch, pybind11 or CUDA-runtime dependency and resolves libcuda.so.1
+ * lazily, so it can be loaded (not launched) on a machine without a driver.
+ *
+ * Conventions: every function returns 0 on success, otherwise a CUresult value
+ * or one of the TK_E_* codes below; nothing throws; tk_last_error() returns a
+ * thread-local description of the most recent failure on the calling thread.
+ * tk_module_launch never synchronises and never allocates, so it may be called
+ * while the stream is being captured into a CUDA graph.
+ */
+#ifndef TRAINKERNEL_RT_H
+#define TRAINKERNEL_RT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TK_E_ARGUMENT 100001   /* null pointer, bad count, bad size */
+#define TK_E_DRIVER   100002   /* libcuda.so.1 or one of its entry points is missing */
+#define TK_E_CAPACITY 100003   /* grid larger than what can be co-resident */
+#define TK_E_KERNEL   100004   /* the kernel reported a timed-out wait; see tk_module_status */
+
+typedef struct tk_module tk_module;   /* owns CUmodule/CUfunction, barrier words, status words */
+
+/* Where a tensor map's base pointer comes from at launch time. */
+enum { TK_BASE_INPUT = 0, TK_BASE_OUTPUT = 1, TK_BASE_WORKSPACE = 2 };
+
+/* Recipe for one 2-D, 128-byte-swizzled tiled tensor map over 16-bit elements. */
+typedef struct {
+    int32_t base_kind;            /* TK_BASE_* */
+    int32_t base_index;           /* input / output index; ignored for the workspace */
+    uint64_t byte_offset;         /* added to the base pointer */
+    uint64_t inner;               /* extent of the unit-stride dimension, in elements */
+    uint64_t outer;               /* extent of the other dimension */
+    uint64_t outer_stride_bytes;  /* multiple of 16 */
+    uint32_t box_inner;           /* 64 */
+    uint32_t box_outer;           /* <= 256 */
+    uint32_t element_bytes;       /* 2 */
+    uint32_t reserved;
+} tk_tensor_map_desc;
+
+/* Load a cubin and look up `entry`.  Replaces the per-kernel pybind module build
+ * (reference: trainkernel/runtime.py:143-152).  `threads` and `dynamic_smem` are the launch
+ * geometry the kernel was generated for; `n_inputs`/`n_outputs` size the pointer tables in the
+ * kernel parameter block (at least one slot each is always laid out). */
+int tk_module_load(const void* cubin, size_t cubin_bytes, const char* entry, int device,
+                   int threads, size_t dynamic_smem, int n_inputs, int n_outputs,
+                   const tk_tensor_map_desc* maps, int n_maps, tk_module** out);
+
+/* Cooperative launch on `stream` (a CUstream / cudaStream_t).  Replaces `launch()`
+ * (reference: trainkernel/codegen.py:863-888).  Pointers are borrowed for the call only. */
+int tk_module_launch(tk_module* module, const void* const* inputs, void* const* outputs,
+                     void* workspace, int grid, void* stream);
+
+/* {registers per thread, local bytes per thread, static + dynamic shared bytes per block,
+ * resident blocks per SM}.  Replaces `resource_usage()` (reference: trainkernel/codegen.py:889-895). */
+int tk_module_resource_usage(tk_module* module, int64_t out[4]);
+
+/* Largest grid a cooperative launch of this kernel accepts on its device. */
+int tk_module_max_coresident_blocks(tk_module* module, int* out);
+
+/* Synchronise `stream`, then copy the kernel's status words {code, stage, block, detail}.
+ * Returns TK_E_KERNEL when code != 0.  (The reference cannot report a stuck barrier:
+ * cooperative_groups grid.sync() has no timeout, reference: trainkernel/codegen.py:833-836.) */
+int tk_module_status(tk_module* module, void* stream, uint32_t out[4]);
+
+/* Clear status and barrier words after an error (synchronises the device context). */
+int tk_module_reset(tk_module* module);
+
+/* Upper bound, in nanoseconds, for any single wait inside the kernel (default 2e9). */
+int tk_module_set_timeout(tk_module* module, uint64_t nanoseconds);
+
+/* Override the arrival count the grid barrier waits for; 0 restores gridDim.x.  Only used by
+ * tests that make a barrier time out on purpose without hanging the device. */
+int tk_module_set_expected_arrivals(tk_module* module, uint32_t arrivals);
+
+/* Synchronise `stream`, then copy up to `count` per-stage %globaltimer stamps written by a
+ * kernel generated with stage stamps (the built-in form of the reference's source-patching
+ * stage profiler, reference: scripts/profile_stages.py:36-54). */
+int tk_module_stage_stamps(tk_module* module, void* stream, uint64_t* out, int count);
+
+void tk_module_unload(tk_module* module);
+
+const char* tk_last_error(void);
+
+/* Number of kernel launches issued through this library by the calling process. */
+uint64_t tk_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

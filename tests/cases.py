@@ -1,0 +1,118 @@
+"""Programs exercised by the GPU parity tests, buildable on any device.
+
+Each case returns `(fn, example_inputs, compile_kind, options)`; inputs are
+created on `device`.  The same list is walked on a CPU-only machine to
+pre-compile every kernel into the in-tree cubin cache (capture only looks at
+shapes, strides and dtypes, so the generated source is identical).
+"""
+from __future__ import annotations
+
+import torch
+
+from trainkernel_b200 import workloads
+
+BF16, F16, F32 = torch.bfloat16, torch.float16, torch.float32
+
+
+def _rand(shape, dtype, device, seed):
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    return torch.randn(shape, generator=gen, dtype=torch.float32).to(dtype).to(device)
+
+
+def gemm_case(m, n, k, a_major, b_major, dtype=BF16):
+    """a @ b with either operand K-major or MN-major in memory."""
+    def build(device):
+        a = _rand((m, k), dtype, device, 1) if a_major == "k" else _rand((k, m), dtype, device, 1).t()
+        b = _rand((n, k), dtype, device, 2).t() if b_major == "k" else _rand((k, n), dtype, device, 2)
+        return (lambda x, y: x @ y), (a, b), "compile", {}
+    return build
+
+
+def workload_case(name, seed=0, **options):
+    def build(device):
+        work = workloads.build(name, seed=seed, device=device)
+        x, t = work.batches[0]
+        return work.fn(), (work.state, x, t), "compile_training", dict(options)
+    return build
+
+
+def native_mlp_case(batch, i, h, o, dtype, **options):
+    """The reference's irregular 2-layer MLP step in one dtype (reference: tests/test_gpu.py:19-28)."""
+    def build(device):
+        gen = torch.Generator(device="cpu").manual_seed(17)
+        def rand(shape):
+            return torch.randn(shape, generator=gen, dtype=dtype).to(device)
+        params = (rand((i, h)) / i ** 0.5, rand((h,)), rand((h, o)) / h ** 0.5, rand((o,)))
+        x, t = rand((batch, i)), rand((batch, o))
+        fn = lambda p, xx, yy: workloads.mlp_native_step(p, xx, yy, 1e-3)  # noqa: E731
+        return fn, (params, x, t), "compile_training", dict(options)
+    return build
+
+
+def function_case(fn, shapes, dtype=F32, kind="compile", **options):
+    def build(device):
+        inputs = tuple(_rand(shape, dtype, device, 10 + i) for i, shape in enumerate(shapes))
+        return fn, inputs, kind, dict(options)
+    return build
+
+
+def _linear_module_case(device):
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(11, 17), torch.nn.ReLU(), torch.nn.Linear(17, 5)).to(device)
+    params = {k: v.detach() for k, v in model.named_parameters()}
+    x, y = _rand((7, 11), F32, device, 3), _rand((7, 5), F32, device, 4)
+
+    def train(p, x, target):
+        def loss(q):
+            return ((torch.func.functional_call(model, q, (x,)) - target) ** 2).mean()
+        grads, value = torch.func.grad_and_value(loss)(p)
+        return value, grads, {key: p[key] - 1e-3 * grads[key] for key in p}
+    return train, (params, x, y), "compile_training", {}
+
+
+CASES = {
+    # tcgen05 GEMM, every operand-major combination, aligned and ragged sizes
+    "gemm_kk_128": gemm_case(128, 128, 128, "k", "k"),
+    "gemm_kn_128": gemm_case(128, 128, 128, "k", "mn"),
+    "gemm_mk_128": gemm_case(128, 128, 128, "mn", "k"),
+    "gemm_mn_128": gemm_case(128, 128, 128, "mn", "mn"),
+    "gemm_kn_ragged": gemm_case(200, 136, 72, "k", "mn"),
+    "gemm_mk_ragged": gemm_case(200, 136, 72, "mn", "k"),
+    "gemm_kn_big": gemm_case(512, 1000, 512, "k", "mn"),
+    "gemm_mn_big": gemm_case(1000, 512, 264, "mn", "mn"),
+    "gemm_kk_big": gemm_case(384, 640, 1024, "k", "k"),
+    "gemm_kn_f16": gemm_case(256, 192, 128, "k", "mn", F16),
+    "gemm_kn_wide": gemm_case(2048, 4096, 256, "k", "mn"),
+    # SIMT and GEMV paths
+    "gemm_f32": gemm_case(65, 67, 17, "k", "mn", F32),
+    "gemm_f32_t": gemm_case(33, 79, 47, "mn", "k", F32),
+    "gemm_odd_bf16": gemm_case(17, 65, 33, "k", "mn"),
+    "gemv_n": gemm_case(1, 200, 128, "k", "mn"),
+    "gemv_k": gemm_case(1, 200, 128, "k", "k"),
+    # BASELINE configurations and the batch-1 pin
+    "c1": workload_case("c1"),
+    "c2": workload_case("c2"),
+    "c2_nofuse": workload_case("c2", fuse_epilogues=False, fuse_pointwise=False),
+    "c2_notc": workload_case("c2", tensor_cores=False),
+    "c3": workload_case("c3"),
+    "c4": workload_case("c4"),
+    "gemv": workload_case("gemv"),
+    # the reference's irregular MLP shapes in each dtype
+    "mlp_f32": native_mlp_case(17, 33, 65, 19, F32),
+    "mlp_bf16": native_mlp_case(17, 33, 65, 19, BF16),
+    "mlp_f16": native_mlp_case(17, 33, 65, 19, F16),
+    "mlp_f32_one_block": native_mlp_case(7, 11, 17, 5, F32, max_blocks=1),
+    "linear_module": _linear_module_case,
+    # general subset
+    "add_one_inplace": function_case(lambda x: x + 1, [(1000,)], inplace_outputs={0: 0}),
+    "partial_reduce": function_case(lambda x: (x.sum((0, 2)), x.mean(1, keepdim=True), x.t().sum(0) if x.dim() == 2 else x.sum()), [(5, 7, 9)]),
+    "big_reduce": function_case(lambda x: (x.sum(), x.mean(0)), [(5003, 3)]),
+    "long_reduce": function_case(lambda x: x.sum(), [(32769,)]),
+    "views_out": function_case(lambda a, b: (a.t(), a + b, a.unsqueeze(0).expand(2, 4, 3), a.contiguous().view(-1)), [(4, 3), (3,)]),
+    "swap_inplace": function_case(lambda a, b: (b * 2.0, a + 1.0), [(64, 3), (64, 3)], inplace_outputs={0: 0, 1: 1}),
+    "transposed_update": function_case(lambda a: a.t() + 1.0, [(32, 32)], inplace_outputs={0: 0}),
+}
+
+
+def build(name: str, device):
+    return CASES[name](device)

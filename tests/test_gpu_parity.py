@@ -1,0 +1,123 @@
+"""GPU parity: every registered case, run through the C-ABI shim, against the CPU oracle."""
+import pytest
+import torch
+from torch.utils._pytree import tree_flatten
+
+from tests import cases
+from tests.helpers import REL_TOL, assert_outputs_close, compile_case, oracle_outputs
+
+pytestmark = pytest.mark.gpu
+
+GEMM_CASES = [name for name in cases.CASES if name.startswith(("gemm_", "gemv_"))]
+STEP_CASES = ["c1", "c2", "c2_nofuse", "c2_notc", "c3", "c4", "gemv", "mlp_f32", "mlp_bf16", "mlp_f16",
+              "mlp_f32_one_block", "linear_module"]
+GENERAL_CASES = ["partial_reduce", "big_reduce", "long_reduce", "views_out"]
+
+
+def _compute_dtype(inputs):
+    flat, _ = tree_flatten(inputs)
+    return torch.float32 if all(t.dtype == torch.float32 for t in flat) else \
+        (torch.float16 if any(t.dtype == torch.float16 for t in flat) else torch.bfloat16)
+
+
+@pytest.mark.parametrize("name", GEMM_CASES)
+def test_gemm_paths_match_oracle(name):
+    compiled, inputs, cpu_inputs, program = compile_case(name)
+    out = compiled(*inputs)
+    compiled.runner.status()
+    # one rounding of the result: 2^-8 for bf16, 2^-11 for f16, accumulation-order noise for fp32
+    tol = {torch.float32: 1e-5, torch.bfloat16: 6e-3, torch.float16: 1e-3}[_compute_dtype(inputs)]
+    assert_outputs_close(out, oracle_outputs(program, cpu_inputs), tol, name)
+
+
+@pytest.mark.parametrize("name", STEP_CASES)
+def test_training_step_matches_oracle(name):
+    compiled, inputs, cpu_inputs, program = compile_case(name)
+    state_leaves, _ = tree_flatten(inputs[0])
+    pointers = [t.data_ptr() for t in state_leaves]
+    expected = oracle_outputs(program, cpu_inputs)      # computed before the step mutates state
+    out = compiled(*inputs)
+    compiled.runner.status()
+    assert_outputs_close(out, expected, REL_TOL[_compute_dtype(inputs)], name)
+    # updated state is written into the caller's state tensors
+    updated, _ = tree_flatten(out[2])
+    assert [t.data_ptr() for t in updated] == pointers
+    n = len(state_leaves)
+    assert_outputs_close(state_leaves, expected[1 + n:], REL_TOL[_compute_dtype(inputs)], name + " state")
+
+
+@pytest.mark.parametrize("name", GENERAL_CASES)
+def test_general_subset_matches_oracle(name):
+    compiled, inputs, cpu_inputs, program = compile_case(name)
+    out = compiled(*inputs)
+    compiled.runner.status()
+    assert_outputs_close(out, oracle_outputs(program, cpu_inputs), 1e-5, name)
+
+
+def test_direct_commit_add_one_and_graph_replay():
+    compiled, inputs, cpu_inputs, _ = compile_case("add_one_inplace")
+    x = inputs[0]
+    original = x.clone()
+    assert compiled.runner.generated.direct_state_commits == 1
+    out = compiled(x)
+    assert out.data_ptr() == x.data_ptr()
+    torch.testing.assert_close(x, original + 1)
+    captured = compiled.capture(x)
+    torch.testing.assert_close(x, original + 1)          # capture restores state
+    for _ in range(4):
+        captured.replay()
+    torch.cuda.synchronize()
+    compiled.runner.status()
+    torch.testing.assert_close(x, original + 5)
+
+
+def test_swap_and_transposed_updates_are_transactional():
+    compiled, inputs, _, _ = compile_case("swap_inplace")
+    a, b = inputs
+    a0, b0 = a.clone(), b.clone()
+    assert compiled.runner.generated.staged_state_commits >= 1
+    compiled(a, b)
+    compiled.runner.status()
+    torch.testing.assert_close(a, b0 * 2.0)
+    torch.testing.assert_close(b, a0 + 1.0)
+    compiled, inputs, _, _ = compile_case("transposed_update")
+    (m,) = inputs
+    m0 = m.clone()
+    assert compiled.runner.generated.direct_state_commits == 0
+    compiled(m)
+    compiled.runner.status()
+    torch.testing.assert_close(m, m0.t() + 1.0)
+
+
+def test_runtime_rejects_mismatched_inputs_and_aliased_buffers():
+    compiled, inputs, _, _ = compile_case("gemm_f32")
+    a, b = inputs
+    with pytest.raises(ValueError, match="shape, stride"):
+        compiled(a[:-1], b)
+    buffers = compiled.runner.allocate(a, b)
+    aliased = type(buffers)(buffers.outputs, a.reshape(-1)[: buffers.workspace.numel()])
+    with pytest.raises(ValueError, match="alias|workspace"):
+        compiled.runner.run_into(a, b, buffers=aliased)
+
+
+def test_barrier_timeout_is_reported_not_hung():
+    """A barrier that can never complete must end with an error status, not a stuck device."""
+    from trainkernel_b200 import runtime
+    compiled, inputs, _, _ = compile_case("c1")
+    runner = compiled.runner
+    lib = runtime.library()
+    assert runner.module.grid > 1
+    lib.tk_module_set_timeout(runner.module.handle, 20_000_000)               # 20 ms
+    lib.tk_module_set_expected_arrivals(runner.module.handle, runner.module.grid + 1)
+    state = inputs[0].clone()
+    compiled(state, inputs[1], inputs[2])
+    with pytest.raises(RuntimeError, match="timed out"):
+        runner.status()
+    # the context is still usable: reset, restore the defaults, run a correct step
+    assert lib.tk_module_reset(runner.module.handle) == 0
+    lib.tk_module_set_expected_arrivals(runner.module.handle, 0)
+    lib.tk_module_set_timeout(runner.module.handle, 2_000_000_000)
+    fresh = inputs[0].clone()
+    out = compiled(fresh, inputs[1], inputs[2])
+    assert runner.status()[0] == 0
+    assert bool(torch.isfinite(out[0]))

@@ -1,0 +1,148 @@
+"""Structural checks of the stage planner and the emitter (CPU only; nvcc cross-compiles)."""
+from math import prod
+
+import pytest
+import torch
+
+import trainkernel_b200 as tk
+from trainkernel_b200 import codegen, runtime, workloads
+from trainkernel_b200.codegen import generate, plan_program
+from trainkernel_b200.plan import ELEMENT_BYTES
+
+
+def _step_program(name):
+    work = workloads.build(name)
+    program, _ = tk.capture(work.fn(), (work.state, *work.batches[0]))
+    n = len(work.state) if isinstance(work.state, tuple) else 1
+    return program, {1 + n + i: i for i in range(n)}
+
+
+def test_tiny_mlp_schedule_shares_stages_and_commits_directly():
+    program, inplace = _step_program("c2")
+    g = generate(program, inplace_outputs=inplace)
+    # weight shadows | fwd 1 | fwd 2 (+loss terms, dY) | dW2, dX, db2, loss | dW1, db1
+    assert g.stages == 5 and g.grid_barriers == 4
+    assert g.tensor_core_operations == 5
+    assert g.direct_state_commits == 4 and g.staged_state_commits == 0
+    assert g.direct_outputs == 9
+    by_stage = {}
+    for stage, kind, name, path, items in g.units:
+        by_stage.setdefault(stage, []).append(name)
+    assert {"mm_2", "mm_3"} <= set(by_stage[3])          # dW and dX of a layer share a stage
+    assert "tcgen05" not in g.source and "tk::gemm_tc<" in g.source   # device library is included, not pasted
+
+
+def test_unfused_schedule_is_longer_and_fp32_master_update_is_fused_when_enabled():
+    program, inplace = _step_program("c2")
+    fused = generate(program, inplace_outputs=inplace)
+    unfused = generate(program, inplace_outputs=inplace, fuse_pointwise=False, fuse_epilogues=False)
+    assert fused.grid_barriers < unfused.grid_barriers
+    assert unfused.inlined_operations == 0
+    assert unfused.materialized_operations == len(program.operations)
+    # fused: the SGD subtraction lives in the dW epilogue functor
+    functor = fused.source[fused.source.index("struct Epi_mm_4"):fused.source.index("extern \"C\"")]
+    assert "P.in[0]" in functor and "P.out[5]" in functor and "P.out[1]" in functor
+
+
+def test_rounding_boundaries_are_kept_in_epilogues():
+    program, inplace = _step_program("c2")
+    g = generate(program, inplace_outputs=inplace)
+    functor = g.source[g.source.index("struct Epi_mm {"):g.source.index("struct Epi_mm_1")]
+    assert functor.count("tk::BF16::rnd") >= 4            # mm, bias cast, add, relu are each rounded
+
+
+def test_workspace_regions_never_overlap_while_live():
+    for name in ("c2", "c4"):
+        program, inplace = _step_program(name)
+        plan = plan_program(program, inplace_outputs=inplace)
+        writer_stage, last_read = {}, {}
+        for unit in plan.units:
+            for store in unit.stores:
+                writer_stage[store.buffer] = unit.stage
+            for buffer in unit.reads:
+                last_read[buffer] = max(last_read.get(buffer, -1), unit.stage)
+        regions = []
+        for buffer, where in plan.storage.items():
+            if where[0] != "ws":
+                continue
+            size = max(1, prod(plan.shapes[buffer])) * ELEMENT_BYTES[plan.dtypes[buffer]]
+            regions.append((where[1], where[1] + size, writer_stage[buffer], max(last_read.get(buffer, -1), writer_stage[buffer]), buffer))
+            assert where[1] % 256 == 0 and where[1] + size <= plan.workspace_bytes
+        for i, a in enumerate(regions):
+            for b in regions[i + 1:]:
+                overlap = a[0] < b[1] and b[0] < a[1]
+                live_together = a[2] <= b[3] and b[2] <= a[3]
+                assert not (overlap and live_together), (a, b)
+
+
+def test_direct_commit_decisions():
+    x = torch.randn(8, 4)
+    program, _ = tk.capture(lambda x: x + 1, (x,))
+    assert generate(program, inplace_outputs={0: 0}).direct_state_commits == 1
+    program, _ = tk.capture(lambda x: x.t() + 1, (torch.randn(4, 4),))
+    g = generate(program, inplace_outputs={0: 0})
+    assert g.direct_state_commits == 0 and g.staged_state_commits == 1
+    a, b = torch.randn(8, 4), torch.randn(8, 4)
+    program, _ = tk.capture(lambda a, b: (b * 2.0, a + 1.0), (a, b))
+    g = generate(program, inplace_outputs={0: 0, 1: 1})
+    assert g.staged_state_commits >= 1                     # a swap cannot be committed in place
+    # returning the old state as well forces the staged path
+    program, _ = tk.capture(lambda x: (x + 1, x), (x,))
+    g = generate(program, inplace_outputs={0: 0})
+    assert g.direct_state_commits == 0
+
+
+def test_option_and_mapping_validation():
+    program, _ = tk.capture(lambda x: x + 1, (torch.randn(8),))
+    with pytest.raises(ValueError, match="max_blocks"):
+        generate(program, max_blocks=0)
+    with pytest.raises(ValueError, match="blocks_per_sm"):
+        generate(program, blocks_per_sm=9)
+    with pytest.raises(ValueError, match="hopper_wgmma"):
+        generate(program, hopper_wgmma=True)
+    with pytest.raises(ValueError, match="invalid inplace"):
+        generate(program, inplace_outputs={3: 0})
+    program2, _ = tk.capture(lambda x, y: (x + 1, y + 1), (torch.randn(8), torch.randn(8)))
+    with pytest.raises(ValueError, match="distinct inputs"):
+        generate(program2, inplace_outputs={0: 0, 1: 0})
+    program3, _ = tk.capture(lambda x: x.t(), (torch.randn(4, 4),))
+    with pytest.raises(ValueError, match="computed values"):
+        generate(program3, inplace_outputs={0: 0})
+    assert generate(program, gemm_k_tile=16, threads_per_block=256).grid >= 1   # reference geometry knobs are ignored
+
+
+def test_path_selection():
+    def paths(fn, *tensors, **options):
+        program, _ = tk.capture(fn, tensors)
+        return [u[3] for u in generate(program, **options).units if u[1] == "gemm"]
+    bf = torch.bfloat16
+    assert paths(lambda a, b: a @ b, torch.randn(64, 64).to(bf), torch.randn(64, 64).to(bf)) == ["tc"]
+    assert paths(lambda a, b: a @ b, torch.randn(64, 64).to(bf), torch.randn(64, 64).to(bf), tensor_cores=False) == ["simt"]
+    assert paths(lambda a, b: a @ b, torch.randn(64, 64), torch.randn(64, 64)) == ["simt"]
+    assert paths(lambda a, b: a @ b, torch.randn(17, 33).to(bf), torch.randn(33, 65).to(bf)) == ["simt"]   # 66-byte rows
+    assert paths(lambda a, b: a @ b, torch.randn(1, 128).to(bf), torch.randn(128, 64).to(bf)) == ["gemv"]
+    assert paths(lambda a, b: a @ b, torch.randn(64, 8).to(bf), torch.randn(8, 64).to(bf)) == ["simt"]     # k <= 8
+
+
+def test_generated_source_is_deterministic_and_compiles_for_sm_100a():
+    program, inplace = _step_program("c2")
+    a = generate(program, inplace_outputs=inplace)
+    b = generate(program, inplace_outputs=inplace)
+    assert a.source == b.source
+    cubin = runtime.build_cubin(a.source)
+    assert cubin[:4] == b"\x7fELF"
+
+
+def test_medium_mlp_plan_fits_and_uses_wide_tiles():
+    sizes, batch = (4096, 8192, 8192, 8192, 4096), 8192
+    state = []
+    for fan_in, fan_out in zip(sizes[:-1], sizes[1:]):
+        state += [torch.empty(fan_in, fan_out, device="meta"), torch.empty(fan_out, device="meta")]
+    x = torch.empty(batch, sizes[0], dtype=torch.bfloat16, device="meta")
+    t = torch.empty(batch, sizes[-1], dtype=torch.bfloat16, device="meta")
+    program, _ = tk.capture(lambda s, x, t: workloads.mlp_master_step(s, x, t, 1e-3), (tuple(state), x, t))
+    g = generate(program, inplace_outputs={9 + i: i for i in range(8)})
+    assert g.tensor_core_operations == 11 and g.direct_state_commits == 8
+    assert g.grid == 148 and g.workspace_bytes < 2 * 2 ** 30
+    assert "tk::gemm_tc<256" in g.source
+    assert len(g.tensor_maps) == 22 and g.param_bytes <= 4096

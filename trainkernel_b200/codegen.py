@@ -1,0 +1,635 @@
+"""CUDA emission for the sm_100a training-step kernel.
+
+`generate(program, **options)` validates the program, plans it (`plan.py`) and
+emits ONE cooperative persistent kernel `tk_step`: stages separated by the
+hand-written grid barrier, dense contractions as `tk::gemm_tc` (tcgen05 + TMEM +
+TMA), `tk::gemm_simt` (exact FP32) or `tk::gemv16` calls with a generated
+epilogue functor, and generated pointwise / reduction loops.  It needs neither
+a GPU nor the CUDA toolkit.  The entry point and the `GeneratedKernel` counters
+keep the reference's names (reference: trainkernel/codegen.py:44-55, 771-815);
+the emitters themselves (reference: codegen.py:339-646, wmma.py, sm90.py,
+gemv.py) are replaced by the sm_100a device library in `csrc/tk_device.cuh`.
+"""
+from __future__ import annotations
+
+import math
+import re
+from dataclasses import dataclass, field
+from math import prod
+
+from .ir import Operation, Program, TensorSpec, row_major, validate
+from .plan import (ELEMENT_BYTES, THREADS, Access, Apply, Const, Load, Plan, Planner, Ref, Unit)
+
+CTYPE = {"float32": "float", "float16": "__half", "bfloat16": "__nv_bfloat16"}
+ROUND = {"float32": "tk::F32", "float16": "tk::F16", "bfloat16": "tk::BF16"}
+
+
+def contiguous_strides(shape: tuple[int, ...]) -> tuple[int, ...]:
+    return row_major(shape)
+
+
+def numel(shape: tuple[int, ...]) -> int:
+    return prod(shape)
+
+
+def _literal(value: int | float) -> str:
+    value = float(value)
+    if not math.isfinite(value):
+        raise ValueError("trainkernel: non-finite scalar constants are unsupported")
+    return f"{value:.17e}f"
+
+
+@dataclass(frozen=True)
+class TensorMapSpec:
+    """Recipe for one CUtensorMap, encoded by the runtime shim at launch time."""
+    base: tuple            # ("in", i) | ("out", slot) | ("ws", byte offset)
+    byte_offset: int       # extra offset from the base pointer
+    inner: int             # extent of the unit-stride dimension (elements)
+    outer: int
+    outer_stride_bytes: int
+    box_inner: int
+    box_outer: int
+
+
+@dataclass(frozen=True)
+class GeneratedKernel:
+    source: str
+    workspace_elements: int               # FP32 elements, as the reference counts workspace
+    materialized_operations: int
+    inlined_operations: int
+    tensor_core_operations: int
+    blocks_per_sm: int
+    max_work_blocks: int
+    grid_barriers: int
+    direct_outputs: int
+    direct_state_commits: int = 0
+    # sm_100a additions
+    entry: str = "tk_step"
+    threads: int = THREADS
+    dynamic_smem: int = 0
+    grid: int = 1
+    tensor_maps: tuple = ()
+    input_count: int = 0
+    output_count: int = 0
+    stages: int = 1
+    units: tuple = ()                     # (stage, kind, name, path, items) per unit, for inspection
+    staged_state_commits: int = 0
+    param_bytes: int = 0
+    workspace_bytes: int = 0
+
+
+class _Body:
+    """Line buffer with indentation and unique temporary names."""
+
+    def __init__(self) -> None:
+        self.lines: list[str] = []
+        self.depth = 0
+        self.counter = 0
+
+    def emit(self, text: str) -> None:
+        self.lines.append("    " * self.depth + text)
+
+    def temp(self, stem: str) -> str:
+        self.counter += 1
+        return f"{stem}{self.counter}"
+
+    def text(self) -> str:
+        return "\n".join(self.lines)
+
+
+class _Emitter:
+    def __init__(self, plan: Plan):
+        self.plan = plan
+        self.maps: list[TensorMapSpec] = []
+        self.functors: list[str] = []
+        self.needs_simt = False
+
+    # -- addressing ------------------------------------------------------------------
+    def pointer(self, buffer: str, dtype: str, const: bool) -> str:
+        where = self.plan.storage[buffer]
+        ctype = CTYPE[dtype]
+        if where[0] == "in":
+            raw = f"P.in[{where[1]}]"
+            return f"reinterpret_cast<const {ctype}*>({raw})" if const else f"reinterpret_cast<{ctype}*>(const_cast<void*>({raw}))"
+        if where[0] == "out":
+            return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>(P.out[{where[1]}])"
+        return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>(P.ws + {where[1]}ULL)"
+
+    @staticmethod
+    def _affine(offset: int, strides: tuple[int, ...], coords: list[str], skip_last: bool) -> str:
+        terms = [f"{offset}LL"] if offset else []
+        last = len(strides) - 1
+        for d, (stride, coord) in enumerate(zip(strides, coords)):
+            if stride == 0 or (skip_last and d == last and False):
+                continue
+            terms.append(f"(int64_t)({coord}) * {stride}LL")
+        return " + ".join(terms) if terms else "0LL"
+
+    # -- expressions -----------------------------------------------------------------
+    def value(self, expr, body: _Body, env: dict, width: str, coords: list[str], nvalid: str) -> str:
+        """Emit code computing `expr` for `width` consecutive elements along the last dim; returns the array name."""
+        key = id(expr)
+        if key in env:
+            return env[key]
+        if isinstance(expr, Ref):
+            return env["ref:" + expr.buffer]
+        if isinstance(expr, Const):
+            name = body.temp("k")
+            body.emit(f"float {name}[{width}];")
+            body.emit(f"_Pragma(\"unroll\") for (int j = 0; j < {width}; ++j) {name}[j] = {_literal(expr.value)};")
+            env[key] = name
+            return name
+        if isinstance(expr, Load):
+            access = expr.access
+            cache_key = ("load", access)
+            if cache_key in env:
+                return env[cache_key]
+            name = body.temp("l")
+            address = self._affine(access.offset, access.strides, coords, False)
+            step = access.strides[-1] if access.strides else 0
+            body.emit(f"float {name}[{width}];")
+            body.emit(f"tk::ld_row_strided<{width}>({self.pointer(access.buffer, access.dtype, True)} + ({address}), {step}LL, {nvalid}, {name});")
+            env[cache_key] = name
+            env[key] = name
+            return name
+        assert isinstance(expr, Apply)
+        op = expr.op
+        args = []
+        for arg in expr.args:
+            if isinstance(arg, Const):
+                args.append(_literal(arg.value))
+            else:
+                args.append(self.value(arg, body, env, width, coords, nvalid) + "[j]")
+        formula = self.formula(op, args)
+        name = body.temp("v")
+        body.emit(f"float {name}[{width}];")
+        body.emit(f"_Pragma(\"unroll\") for (int j = 0; j < {width}; ++j) {name}[j] = {ROUND[op.output.dtype]}::rnd({formula});")
+        env[key] = name
+        return name
+
+    @staticmethod
+    def formula(op: Operation, a: list[str]) -> str:
+        kind = op.op
+        if kind in ("add", "sub"):
+            sign = "+" if kind == "add" else "-"
+            return f"({a[0]} {sign} ({_literal(op.attrs.get('alpha', 1))} * {a[1]}))"
+        if kind == "mul":
+            return f"({a[0]} * {a[1]})"
+        if kind == "div":
+            return f"({a[0]} / {a[1]})"
+        if kind == "neg":
+            return f"(-({a[0]}))"
+        if kind == "relu":
+            return f"tk::relu({a[0]})"
+        if kind == "pow":
+            exponent = op.inputs[1] if len(op.inputs) > 1 else op.attrs.get("exponent", 2)
+            if not isinstance(exponent, (int, float)):
+                raise ValueError("trainkernel: pow exponent must be a scalar")
+            if exponent == 2:
+                return f"({a[0]} * {a[0]})"
+            if exponent == 1:
+                return f"({a[0]})"
+            return f"powf({a[0]}, {_literal(exponent)})"
+        if kind == "threshold_backward":
+            return f"(({a[1]} <= {_literal(op.attrs.get('threshold', 0))}) ? 0.0f : {a[0]})"
+        if kind == "full":
+            return _literal(op.attrs.get("value", op.inputs[0] if op.inputs else 0))
+        if kind == "cast":
+            return a[0]
+        raise ValueError(f"trainkernel: unsupported pointwise operation {kind}")
+
+    def dag(self, unit: Unit, body: _Body, env: dict, width: str, coords: list[str], nvalid: str) -> None:
+        """Members in order, then the unit's stores, for `width` elements at `coords`."""
+        for member in unit.members:
+            buffer = member.output.buffer
+            env["ref:" + buffer] = self.value(unit.exprs[buffer], body, env, width, coords, nvalid)
+        dense = row_major(unit.dims)
+        for store in unit.stores:
+            if unit.phase == "partial":
+                continue
+            address = self._affine(0, dense, coords, False)
+            body.emit(f"tk::st_row<{width}>({self.pointer(store.buffer, store.dtype, False)} + ({address}), {nvalid}, {env['ref:' + store.buffer]});")
+
+    # -- units -------------------------------------------------------------------------
+    def functor(self, unit: Unit) -> str:
+        """Epilogue functor of a GEMM unit: rounds the accumulator, runs the DAG, stores."""
+        op = unit.root
+        name = f"Epi_{unit.name}"
+        body = _Body()
+        body.depth = 2
+        env: dict = {}
+        coords = ["x0", "x1"]
+        root = body.temp("v")
+        rounding = ROUND[op.output.dtype]
+        if op.op == "addmm":
+            alpha, beta = op.attrs.get("alpha", 1), op.attrs.get("beta", 1)
+            if unit.bias is not None:
+                bias = self.value(unit.bias, body, env, "W", coords, "nvalid")
+            if alpha == 0 and beta == 0:
+                combine = "0.0f"
+            elif beta == 0:
+                combine = f"({_literal(alpha)} * (acc[j]))"
+            elif alpha == 0:
+                combine = f"({_literal(beta)} * ({bias}[j]))"
+            else:
+                combine = f"({_literal(alpha)} * (acc[j]) + {_literal(beta)} * ({bias}[j]))"
+        else:
+            combine = "acc[j]"
+        body.emit(f"float {root}[W];")
+        body.emit(f"_Pragma(\"unroll\") for (int j = 0; j < W; ++j) {root}[j] = {rounding}::rnd({combine});")
+        env["ref:" + op.output.buffer] = root
+        self.dag(unit, body, env, "W", coords, "nvalid")
+        self.functors.append(
+            f"struct {name} {{\n"
+            f"    template <int W> static __device__ __forceinline__ void run(const Params& P, int x0, int x1, int nvalid, const float* acc) {{\n"
+            f"{body.text()}\n"
+            f"    }}\n}};\n")
+        return name
+
+    def _tensor_map(self, operand, rows: int, depth: int, box_rows: int) -> tuple[int, bool]:
+        """Register a tensor map for a [rows, depth] operand; returns (index, is_mn_major)."""
+        s_row, s_k = operand.strides
+        k_major = (s_k == 1 or depth == 1) and s_row % 8 == 0 and (s_row >= depth or rows == 1)
+        base = self.plan.storage[operand.buffer]
+        if k_major:
+            spec = TensorMapSpec(base, operand.offset * 2, depth, rows, max(s_row, 8) * 2, 64, box_rows)
+        else:
+            spec = TensorMapSpec(base, operand.offset * 2, rows, depth, max(s_k, 8) * 2, 64, 64)
+        self.maps.append(spec)
+        return len(self.maps) - 1, not k_major
+
+    def gemm(self, unit: Unit, body: _Body, base: int) -> None:
+        epi = self.functor(unit)
+        m, n, k = unit.mnk
+        a, b = unit.a, unit.b
+        if unit.path == "tc":
+            ia, a_mn = self._tensor_map(a, m, k, 128)
+            # B is [K, N]: its "rows" are N and strides are (stride along N, stride along K)
+            flipped = type(b)(b.buffer, b.dtype, b.round_to, b.offset, (b.strides[1], b.strides[0]))
+            ib, b_mn = self._tensor_map(flipped, n, k, unit.block_n)
+            fmt = 1 if a.dtype == "bfloat16" else 0
+            body.emit(f"tk::gemm_tc<{unit.block_n}, {str(a_mn).lower()}, {str(b_mn).lower()}, {fmt}, {epi}>"
+                      f"(c, P, &P.maps[{ia}], &P.maps[{ib}], {m}, {n}, {k}, {base}LL);")
+        elif unit.path == "gemv":
+            k_major = b.strides[0] == 1 and b.strides[1] != 1
+            ld = b.strides[1] if k_major else b.strides[0]
+            body.emit(f"tk::gemv<{CTYPE[a.dtype]}, {ROUND[a.round_to]}, {CTYPE[b.dtype]}, {ROUND[b.round_to]}, {str(k_major).lower()}, {epi}>(c, P, "
+                      f"{self.pointer(a.buffer, a.dtype, True)} + {a.offset}LL, {a.strides[1]}LL, "
+                      f"{self.pointer(b.buffer, b.dtype, True)} + {b.offset}LL, {ld}LL, {n}, {k}, {base}LL);")
+        else:
+            self.needs_simt = True
+            body.emit(f"tk::gemm_simt<{CTYPE[a.dtype]}, {ROUND[a.round_to]}, {CTYPE[b.dtype]}, {ROUND[b.round_to]}, {epi}>(c, P, &simt, "
+                      f"{self.pointer(a.buffer, a.dtype, True)} + {a.offset}LL, {a.strides[0]}LL, {a.strides[1]}LL, "
+                      f"{self.pointer(b.buffer, b.dtype, True)} + {b.offset}LL, {b.strides[0]}LL, {b.strides[1]}LL, {m}, {n}, {k}, {base}LL);")
+
+    @staticmethod
+    def _unravel(flat: str, dims: tuple[int, ...], prefix: str, body: _Body) -> list[str]:
+        names = []
+        dense = row_major(dims)
+        for d, (extent, stride) in enumerate(zip(dims, dense)):
+            name = f"{prefix}{d}"
+            if extent == 1:
+                body.emit(f"const int64_t {name} = 0;")
+            elif d == 0:
+                body.emit(f"const int64_t {name} = ({flat}) / {stride}LL;")
+            else:
+                body.emit(f"const int64_t {name} = (({flat}) / {stride}LL) % {extent}LL;")
+            names.append(name)
+        return names
+
+    def _flat_ok(self, unit: Unit) -> bool:
+        dense = row_major(unit.dims)
+        live = [d for d, n in enumerate(unit.dims) if n > 1]
+        found: list[Access] = []
+
+        def walk(expr) -> None:
+            if isinstance(expr, Load):
+                found.append(expr.access)
+            elif isinstance(expr, Apply):
+                for arg in expr.args:
+                    walk(arg)
+
+        for expr in unit.exprs.values():
+            walk(expr)
+        return all(all(a.strides[d] == dense[d] for d in live) or not any(a.strides[d] for d in live) for a in found)
+
+    def point(self, unit: Unit, body: _Body, base: int) -> None:
+        total = prod(unit.dims)
+        if total == 0:
+            return
+        body.emit(f"// {unit.name}: pointwise over {list(unit.dims)}")
+        if self._flat_ok(unit):
+            # collapse to one dimension, 8 consecutive elements per thread
+            flat = Unit(unit.kind, unit.name, unit.index, (total,))
+            flat.members, flat.stores = unit.members, unit.stores
+            dense = row_major(unit.dims)
+            live = [d for d, n in enumerate(unit.dims) if n > 1]
+
+            def rebase(expr):
+                if isinstance(expr, Load):
+                    a = expr.access
+                    unit_stride = 1 if live and all(a.strides[d] == dense[d] for d in live) else 0
+                    if not live:
+                        unit_stride = 0
+                    return Load(Access(a.buffer, a.dtype, a.offset, (unit_stride,)))
+                if isinstance(expr, Apply):
+                    return Apply(expr.op, tuple(rebase(arg) for arg in expr.args))
+                return expr
+
+            flat.exprs = {k: rebase(v) for k, v in unit.exprs.items()}
+            body.emit(f"for (int64_t it = tk::first_item({base}LL); it < {unit.items}LL; it += gridDim.x) {{")
+            body.depth += 1
+            body.emit(f"const int64_t i0 = (it * {THREADS}LL + threadIdx.x) * 8;")
+            body.emit(f"if (i0 < {total}LL) {{")
+            body.depth += 1
+            body.emit(f"const int nvalid = (int)tk::imin(8, {total}LL - i0);")
+            self.dag(flat, body, {}, "8", ["i0"], "nvalid")
+            body.depth -= 1
+            body.emit("}")
+            body.depth -= 1
+            body.emit("}")
+            return
+        body.emit(f"for (int64_t it = tk::first_item({base}LL); it < {unit.items}LL; it += gridDim.x) {{")
+        body.depth += 1
+        body.emit(f"for (int64_t i = it * {THREADS * 8}LL + threadIdx.x; i < tk::imin((it + 1) * {THREADS * 8}LL, {total}LL); i += {THREADS}) {{")
+        body.depth += 1
+        coords = self._unravel("i", unit.dims, "x", body)
+        self.dag(unit, body, {}, "1", coords, "1")
+        body.depth -= 1
+        body.emit("}")
+        body.depth -= 1
+        body.emit("}")
+
+    def _finish_value(self, unit: Unit, body: _Body, acc: str, env: dict) -> None:
+        op = unit.root
+        size = prod(unit.reduced)
+        value = acc if op.op == "sum" else (f"({acc} / {size}.0f)" if size else "NAN")
+        root = body.temp("v")
+        body.emit(f"float {root}[1] = {{{ROUND[op.output.dtype]}::rnd({value})}};")
+        env["ref:" + op.output.buffer] = root
+
+    def reduce(self, unit: Unit, body: _Body, base: int) -> None:
+        outputs, size, parts = prod(unit.kept), prod(unit.reduced), unit.parts
+        chunk = -(-size // parts)
+        kept_rank = len(unit.kept)
+        body.emit(f"// {unit.name}: {unit.root.op} {list(unit.kept)} <- {list(unit.reduced)} ({unit.strategy or 'finish'}, parts={parts})")
+        scratch = None
+        if unit.scratch:
+            scratch = self.pointer(unit.scratch, "float32", unit.phase == "finish")
+        if unit.phase == "finish":
+            body.emit(f"for (int64_t it = tk::first_item({base}LL); it < {unit.items}LL; it += gridDim.x) {{")
+            body.depth += 1
+            body.emit(f"const int64_t o = it * {THREADS}LL + threadIdx.x;")
+            body.emit(f"if (o < {outputs}LL) {{")
+            body.depth += 1
+            body.emit("float acc = 0.0f;")
+            body.emit(f"for (int p = 0; p < {parts}; ++p) acc += {scratch}[(int64_t)p * {outputs}LL + o];")
+            env: dict = {}
+            self._finish_value(unit, body, "acc", env)
+            coords = self._unravel("o", unit.kept, "x", body)
+            self.dag(unit, body, env, "1", coords, "1")
+            body.depth -= 1
+            body.emit("}")
+            body.depth -= 1
+            body.emit("}")
+            return
+
+        def accumulate(r_expr: str) -> None:
+            names = self._unravel(r_expr, unit.reduced, "r", body)
+            env2: dict = {}
+            value = self.value(unit.source, body, env2, "1", kcoords + names, "1")
+            body.emit(f"acc += {value}[0];")
+
+        if unit.strategy == "thread":
+            body.emit(f"for (int64_t it = tk::first_item({base}LL); it < {unit.items}LL; it += gridDim.x) {{")
+            body.depth += 1
+            body.emit(f"const int64_t o = (it / {parts}) * {THREADS}LL + threadIdx.x;")
+            body.emit(f"const int part = (int)(it % {parts});")
+            body.emit(f"if (o < {outputs}LL) {{")
+            body.depth += 1
+            kcoords = self._unravel("o", unit.kept, "x", body)
+            body.emit("float acc = 0.0f;")
+            body.emit(f"const int64_t r_end = tk::imin((int64_t)(part + 1) * {chunk}LL, {size}LL);")
+            body.emit(f"for (int64_t r = (int64_t)part * {chunk}LL; r < r_end; ++r) {{")
+            body.depth += 1
+            accumulate("r")
+            body.depth -= 1
+            body.emit("}")
+            if unit.phase == "partial":
+                body.emit(f"{scratch}[(int64_t)part * {outputs}LL + o] = acc;")
+            else:
+                env = {}
+                self._finish_value(unit, body, "acc", env)
+                self.dag(unit, body, env, "1", kcoords, "1")
+            body.depth -= 1
+            body.emit("}")
+            body.depth -= 1
+            body.emit("}")
+            return
+        # block strategy: one (output, part) per block iteration, all threads stride the reduced range
+        body.emit(f"for (int64_t it = tk::first_item({base}LL); it < {unit.items}LL; it += gridDim.x) {{")
+        body.depth += 1
+        body.emit(f"const int64_t o = it / {parts};")
+        body.emit(f"const int part = (int)(it % {parts});")
+        kcoords = self._unravel("o", unit.kept, "x", body)
+        body.emit("float acc = 0.0f;")
+        body.emit(f"const int64_t r_end = tk::imin((int64_t)(part + 1) * {chunk}LL, {size}LL);")
+        body.emit(f"for (int64_t r = (int64_t)part * {chunk}LL + threadIdx.x; r < r_end; r += {THREADS}) {{")
+        body.depth += 1
+        accumulate("r")
+        body.depth -= 1
+        body.emit("}")
+        body.emit("acc = tk::block_sum(c, acc);")
+        body.emit("if (threadIdx.x == 0) {")
+        body.depth += 1
+        if unit.phase == "partial":
+            body.emit(f"{scratch}[(int64_t)part * {outputs}LL + o] = acc;")
+        else:
+            env = {}
+            self._finish_value(unit, body, "acc", env)
+            self.dag(unit, body, env, "1", kcoords, "1")
+        body.depth -= 1
+        body.emit("}")
+        body.depth -= 1
+        body.emit("}")
+
+    # -- whole kernel ------------------------------------------------------------------
+    def kernel(self, stage_stamps: bool) -> str:
+        plan = self.plan
+        body = _Body()
+        body.depth = 1
+        for stage in range(plan.stages):
+            if stage:
+                body.emit("tk::grid_barrier(c);")
+                if stage_stamps:
+                    body.emit(f"if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[{stage}] = tk::global_timer_ns();")
+            body.emit(f"// ---- stage {stage} ----")
+            base = 0
+            members = [u for u in plan.units if u.stage == stage]
+            # GEMM units first: the specialised warps drain them before joining the block-wide loops
+            for unit in sorted(members, key=lambda u: (u.kind != "gemm", u.path != "tc", u.index)):
+                body.emit("{")
+                body.depth += 1
+                if unit.kind == "gemm":
+                    body.emit(f"// {unit.name}: {unit.root.op} {unit.mnk} via {unit.path}")
+                    self.gemm(unit, body, base)
+                elif unit.kind == "reduce":
+                    self.reduce(unit, body, base)
+                else:
+                    self.point(unit, body, base)
+                body.depth -= 1
+                body.emit("}")
+                base += unit.items
+        n_in = max(1, len(plan.program.inputs))
+        n_out = max(1, len(plan.program.outputs))
+        n_maps = max(1, len(self.maps))
+        use_tc = "true" if plan.uses_tc else "false"
+        header = [
+            '#include "tk_device.cuh"',
+            "struct Params {",
+            f"    CUtensorMap maps[{n_maps}];",
+            f"    const void* in[{n_in}];",
+            f"    void* out[{n_out}];",
+            "    uint8_t* ws;",
+            "    uint32_t* sync;",
+            "    uint32_t* status;",
+            "    uint64_t* stamps;",
+            "    uint64_t timeout_ns;",
+            "    uint32_t arrivals;",
+            "    uint32_t reserved;",
+            "};",
+            "",
+        ]
+        entry = [
+            f"extern \"C\" __global__ void __launch_bounds__({THREADS}, 1) tk_step(const __grid_constant__ Params P) {{",
+            "    extern __shared__ uint8_t dyn_smem[];",
+            "    __shared__ tk::SharedState shared_state;",
+        ]
+        if self.needs_simt:
+            entry.append("    __shared__ tk::SimtSmem simt;")
+        entry += [
+            "    tk::Ctx c;",
+            f"    tk::ctx_init(c, P.sync, P.status, P.timeout_ns, P.arrivals, &shared_state, dyn_smem, {use_tc});",
+        ]
+        if stage_stamps:
+            entry.append("    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[0] = tk::global_timer_ns();")
+        tail = []
+        if stage_stamps:
+            tail.append(f"    __syncthreads();\n    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[{plan.stages}] = tk::global_timer_ns();")
+        tail += [f"    tk::ctx_finish(c, {use_tc});", "}", ""]
+        return "\n".join(header + self.functors + entry + [body.text()] + tail)
+
+
+def _check_names(program: Program) -> None:
+    for spec in (*program.inputs, *(op.output for op in program.operations), *program.outputs):
+        if spec.dtype not in CTYPE:
+            raise ValueError(f"trainkernel: unsupported CUDA dtype {spec.dtype}")
+        if not re.fullmatch(r"[A-Za-z_][A-Za-z_0-9]*", spec.buffer):
+            raise ValueError("trainkernel: invalid buffer identifier")
+
+
+def _check_broadcasts(program: Program) -> None:
+    for op in program.operations:
+        if op.op in ("mm", "addmm", "sum", "mean"):
+            continue
+        for value in op.inputs:
+            if not isinstance(value, TensorSpec):
+                continue
+            if len(value.shape) > len(op.output.shape):
+                raise ValueError("trainkernel: invalid broadcast rank")
+            tail = op.output.shape[len(op.output.shape) - len(value.shape):] if value.shape else ()
+            if any(a != 1 and a != b for a, b in zip(value.shape, tail)):
+                raise ValueError("trainkernel: incompatible broadcast dimensions")
+
+
+def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = None, fuse_pointwise: bool = True,
+                 fuse_epilogues: bool = True, max_blocks: int | None = None, tensor_cores: bool = True,
+                 block_n: int | None = None) -> Plan:
+    """Validate, canonicalise and plan `program` (no code is emitted)."""
+    validate(program)
+    from .passes import canonicalize_transposed_mm
+    program = canonicalize_transposed_mm(program)
+    validate(program)
+    _check_names(program)
+    _check_broadcasts(program)
+    if max_blocks is not None and (type(max_blocks) is not int or max_blocks < 1):
+        raise ValueError("trainkernel: max_blocks must be positive when provided")
+    if block_n is not None and block_n not in (64, 128, 256):
+        raise ValueError("trainkernel: block_n must be 64, 128 or 256")
+    mapping = dict(inplace_outputs or {})
+    if any(type(i) is not int or type(j) is not int or not 0 <= i < len(program.outputs) or not 0 <= j < len(program.inputs)
+           for i, j in mapping.items()):
+        raise ValueError("trainkernel: invalid inplace output/input index")
+    if len(set(mapping.values())) != len(mapping):
+        raise ValueError("trainkernel: inplace outputs must target distinct inputs")
+    produced = {op.output.buffer for op in program.operations}
+    for slot, target in mapping.items():
+        output, source = program.outputs[slot], program.inputs[target]
+        if output.shape != source.shape or output.dtype != source.dtype or source.strides != row_major(source.shape):
+            raise ValueError("trainkernel: inplace output must match a contiguous input shape and dtype")
+        if output.buffer not in produced:
+            raise ValueError("trainkernel: inplace outputs must be computed values, not input views")
+    return Planner(program, inplace_outputs=mapping, fuse_pointwise=fuse_pointwise, fuse_epilogues=fuse_epilogues,
+                   max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n).plan()
+
+
+_IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shared_skew", "split_k_gemv",
+                            "threads_per_block", "inline_input_casts")
+
+
+def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: bool = True,
+             max_blocks: int | None = None, inplace_outputs: dict[int, int] | None = None,
+             tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
+             **reference_knobs) -> GeneratedKernel:
+    """Generate the sm_100a kernel source and launch metadata for `program`.
+
+    The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
+    `gemm_tile_n`, `shared_skew`, `split_k_gemv`, `threads_per_block`,
+    `inline_input_casts`) have no meaning on this back end; they are accepted so
+    existing call sites keep working, and ignored.  `hopper_wgmma=True` is rejected.
+    """
+    if reference_knobs.pop("hopper_wgmma", False):
+        raise ValueError("trainkernel: hopper_wgmma is an SM90a option; this back end targets sm_100a")
+    unknown = set(reference_knobs) - set(_IGNORED_REFERENCE_KNOBS)
+    if unknown:
+        raise TypeError(f"trainkernel: unknown option(s) {sorted(unknown)}")
+    blocks_per_sm = reference_knobs.get("blocks_per_sm", 1)
+    if type(blocks_per_sm) is not int or not 1 <= blocks_per_sm <= 8:
+        raise ValueError("trainkernel: blocks_per_sm must be between 1 and 8")
+    plan = plan_program(program, inplace_outputs=inplace_outputs, fuse_pointwise=fuse_pointwise,
+                        fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n)
+    emitter = _Emitter(plan)
+    source = emitter.kernel(stage_stamps)
+    n_in, n_out = max(1, len(plan.program.inputs)), max(1, len(plan.program.outputs))
+    n_maps = max(1, len(emitter.maps))
+    param_bytes = 128 * n_maps + 8 * (n_in + n_out) + 8 * 6
+    per_stage: dict[int, int] = {}
+    for unit in plan.units:
+        per_stage[unit.stage] = per_stage.get(unit.stage, 0) + unit.items
+    materialized = sum((1 if u.root is not None and u.phase != "partial" else 0) + len(u.members) for u in plan.units)
+    from .plan import SM_COUNT  # noqa: F401
+    dyn = 0
+    if plan.uses_tc:
+        dyn = 4 * (128 * 64 * 2 + 256 * 64 * 2) + 1024
+    return GeneratedKernel(
+        source=source,
+        workspace_elements=-(-plan.workspace_bytes // 4),
+        materialized_operations=materialized,
+        inlined_operations=len(plan.inlined),
+        tensor_core_operations=plan.tensor_core_units,
+        blocks_per_sm=1,
+        max_work_blocks=max(per_stage.values(), default=1),
+        grid_barriers=plan.stages - 1,
+        direct_outputs=len(plan.native_outputs) + len(plan.direct_commits),
+        direct_state_commits=len(plan.direct_commits),
+        dynamic_smem=dyn,
+        grid=plan.grid,
+        tensor_maps=tuple(emitter.maps),
+        input_count=len(plan.program.inputs),
+        output_count=len(plan.program.outputs),
+        stages=plan.stages,
+        units=tuple((u.stage, u.kind + (":" + u.phase if u.phase else ""), u.name, u.path, u.items) for u in plan.units),
+        staged_state_commits=len(plan.staged_commits),
+        param_bytes=param_bytes,
+        workspace_bytes=plan.workspace_bytes,
+    )

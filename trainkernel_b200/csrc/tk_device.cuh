@@ -1,0 +1,612 @@
+// Device-side building blocks of the generated sm_100a training-step kernel.
+//
+// The generator emits one persistent cooperative kernel per program and glues
+// these pieces together: a hand-written grid barrier, a warp-specialised
+// tcgen05 GEMM pipeline (TMA -> swizzled shared memory -> tcgen05.mma -> TMEM ->
+// tcgen05.ld epilogue), an exact-FP32 SIMT GEMM, a GEMV, and row helpers used
+// by the generated pointwise / reduction / epilogue code.
+//
+// Every wait in this file is bounded by a wall-clock limit.  When a limit is
+// hit the kernel records {code, stage, block, detail} in the status words,
+// raises a block-wide and grid-wide abort flag, skips the remaining work and
+// returns normally, so the CUDA context stays usable and the host can report.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace tk {
+
+constexpr int kThreads = 192;          // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int kEpiThreads = 128;
+constexpr int BM = 128;                // UMMA M
+constexpr int BK = 64;                 // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kMaxBN = 256;
+constexpr int kSlotA = BM * BK * 2;    // 16 KiB
+constexpr int kSlotB = kMaxBN * BK * 2;  // 32 KiB
+constexpr int kSlotBytes = kSlotA + kSlotB;
+constexpr int kTmemCols = 512;         // two 256-column FP32 accumulators
+constexpr int kDynSmem = kStages * kSlotBytes + 1024;  // +1024 for manual alignment
+
+enum : uint32_t {
+    kOk = 0,
+    kErrGridBarrier = 1,
+    kErrSmemFull = 2,     // MMA issuer waited for TMA data
+    kErrSmemEmpty = 3,    // producer waited for a free slot
+    kErrTmemFull = 4,     // epilogue waited for the accumulator
+    kErrTmemEmpty = 5,    // MMA issuer waited for the epilogue to drain
+    kErrPeerFlag = 6,     // cross-GPU flag wait
+};
+
+// ----------------------------------------------------------------------------
+// small PTX wrappers
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ uint64_t global_timer_ns() { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) { uint32_t v; asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
+__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p) { uint32_t v; asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) { asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ void st_relaxed_gpu(uint32_t* p, uint32_t v) { asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t atom_add_acq_rel_gpu(uint32_t* p, uint32_t v) { uint32_t old; asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory"); return old; }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+    return pred != 0;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count)); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory"); }
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) { asm volatile("prefetch.tensormap [%0];" :: "l"(map) : "memory"); }
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 32 consecutive FP32 columns: thread i of the warp receives row (lane base + i).
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (128-byte swizzle, sm_100 version bit set).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;     // descriptor version for sm_100
+    d |= 2ull << 61;     // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor for kind::f16 with FP32 accumulation.  fmt: 0 = f16, 1 = bf16.  major: 0 = K, 1 = MN.
+__host__ __device__ constexpr uint32_t umma_idesc(int fmt, int a_major, int b_major, int m, int n) {
+    return (1u << 4) | (uint32_t(fmt) << 7) | (uint32_t(fmt) << 10) | (uint32_t(a_major) << 15) | (uint32_t(b_major) << 16) |
+           (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+// ----------------------------------------------------------------------------
+// per-CTA context
+// ----------------------------------------------------------------------------
+struct SharedState {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort;
+    float reduce[32];
+};
+
+struct Ctx {
+    uint32_t* sync;        // {count, generation} of this launch's barrier slot
+    uint32_t* status;      // {code, stage, block, detail}
+    uint64_t timeout_ns;
+    uint32_t arrivals;     // blocks the grid barrier waits for (gridDim.x unless a test overrides it)
+    SharedState* sh;
+    uint8_t* slots;        // 1024-byte aligned pipeline slots
+    uint32_t stage_id;
+    // pipeline cursors; each role advances its own copy through the same tile sequence
+    uint32_t slot, slot_phase;     // smem ring position and parity
+    uint32_t acc, acc_phase;       // accumulator buffer and parity
+    uint32_t tmem;
+    int warp, lane;
+
+    __device__ __forceinline__ bool aborted() const { return *reinterpret_cast<volatile uint32_t*>(&sh->abort) != 0; }
+    __device__ __forceinline__ bool grid_aborted() const { return ld_relaxed_gpu(status) != 0; }
+    __device__ __noinline__ void fail(uint32_t code, uint32_t detail) {
+        if (atomicCAS(status, 0u, code) == 0u) {
+            status[1] = stage_id;
+            status[2] = blockIdx.x;
+            status[3] = detail;
+            __threadfence();
+        }
+        *reinterpret_cast<volatile uint32_t*>(&sh->abort) = 1u;
+    }
+    // Bounded mbarrier wait.  Returns false when the block is aborting.
+    __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, uint32_t code) {
+        for (int spin = 0; spin < 64; ++spin)
+            if (mbar_try(bar, parity)) return true;
+        const uint64_t start = global_timer_ns();
+        uint32_t polls = 0;
+        while (!mbar_try(bar, parity)) {
+            if (aborted()) return false;
+            if ((++polls & 0x3F) == 0) {
+                if (grid_aborted()) { *reinterpret_cast<volatile uint32_t*>(&sh->abort) = 1u; return false; }
+                if (global_timer_ns() - start > timeout_ns) { fail(code, parity); return false; }
+            }
+        }
+        return true;
+    }
+    __device__ __forceinline__ void advance_slot() { if (++slot == kStages) { slot = 0; slot_phase ^= 1; } }
+    __device__ __forceinline__ void advance_acc() { if (++acc == 2) { acc = 0; acc_phase ^= 1; } }
+};
+
+__device__ __forceinline__ void ctx_init(Ctx& c, uint32_t* sync, uint32_t* status, uint64_t timeout_ns, uint32_t arrivals, SharedState* sh, uint8_t* dyn, bool use_tc) {
+    c.sync = sync; c.status = status; c.timeout_ns = timeout_ns; c.sh = sh;
+    c.arrivals = arrivals ? arrivals : gridDim.x;
+    c.slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
+    c.stage_id = 0; c.slot = 0; c.slot_phase = 0; c.acc = 0; c.acc_phase = 0; c.tmem = 0;
+    c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        sh->abort = 0;
+        for (int i = 0; i < kStages; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sh->tmem_full[i], 1); mbar_init(&sh->tmem_empty[i], kEpiThreads / 32); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (use_tc && c.warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&sh->tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (use_tc) c.tmem = *reinterpret_cast<volatile uint32_t*>(&sh->tmem_base);
+}
+
+__device__ __forceinline__ void ctx_finish(Ctx& c, bool use_tc) {
+    tc_fence_before();
+    __syncthreads();
+    if (c.aborted()) {
+        // Give TMA copies that nobody waited for time to land before shared memory is released.
+        const uint64_t start = global_timer_ns();
+        while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (use_tc && c.warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(c.tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ----------------------------------------------------------------------------
+// grid barrier: atomic arrive, generation spin, release/acquire at GPU scope.
+// The counter resets itself, so any number of launches and CUDA-graph replays
+// can reuse the same two words without host intervention.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void grid_barrier(Ctx& c) {
+    fence_proxy_async();       // generic-proxy writes of this stage before later TMA reads
+    __syncthreads();
+    if (c.arrivals > 1 && threadIdx.x == 0 && !c.aborted()) {
+        uint32_t* count = c.sync;
+        uint32_t* gen = c.sync + 1;
+        const uint32_t my_gen = ld_relaxed_gpu(gen);
+        const uint32_t arrived = atom_add_acq_rel_gpu(count, 1u);
+        if (arrived == c.arrivals - 1) {
+            st_relaxed_gpu(count, 0u);
+            st_release_gpu(gen, my_gen + 1u);
+        } else {
+            uint32_t polls = 0;
+            uint64_t start = 0;
+            while (ld_acquire_gpu(gen) == my_gen) {
+                if ((++polls & 0xFF) == 0) {
+                    if (start == 0) start = global_timer_ns();
+                    if (c.grid_aborted()) { *reinterpret_cast<volatile uint32_t*>(&c.sh->abort) = 1u; break; }
+                    if (global_timer_ns() - start > c.timeout_ns) { c.fail(kErrGridBarrier, arrived); break; }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    fence_proxy_async();
+    ++c.stage_id;
+}
+
+// ----------------------------------------------------------------------------
+// rounding helpers: every IR value is rounded to its declared dtype
+// ----------------------------------------------------------------------------
+struct F32 { using T = float; static __device__ __forceinline__ float rnd(float x) { return x; } };
+struct BF16 { using T = __nv_bfloat16; static __device__ __forceinline__ float rnd(float x) { return __bfloat162float(__float2bfloat16_rn(x)); } };
+struct F16 { using T = __half; static __device__ __forceinline__ float rnd(float x) { return __half2float(__float2half_rn(x)); } };
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
+__device__ __forceinline__ void from_f32(float* p, float x) { *p = x; }
+__device__ __forceinline__ void from_f32(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
+__device__ __forceinline__ void from_f32(__half* p, float x) { *p = __float2half_rn(x); }
+
+__device__ __forceinline__ int64_t imin(int64_t a, int64_t b) { return a < b ? a : b; }
+__device__ __forceinline__ float relu(float x) { return x < 0.0f ? 0.0f : x; }   // keeps NaN like torch.relu
+
+// W consecutive elements starting at p -> FP32.  Vector loads when p is 16-byte aligned and all W are valid.
+template <int W>
+__device__ __forceinline__ void ld_row(const float* p, int nvalid, float* out) {
+    if constexpr (W % 4 == 0) {
+        if (nvalid >= W && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < W; j += 4) {
+                const float4 v = *reinterpret_cast<const float4*>(p + j);
+                out[j] = v.x; out[j + 1] = v.y; out[j + 2] = v.z; out[j + 3] = v.w;
+            }
+            return;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < W; ++j) out[j] = j < nvalid ? p[j] : 0.0f;
+}
+template <int W, typename T16>
+__device__ __forceinline__ void ld_row16(const T16* p, int nvalid, float* out) {
+    if constexpr (W % 8 == 0) {
+        if (nvalid >= W && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < W; j += 8) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(p + j);
+                const T16* h = reinterpret_cast<const T16*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) out[j + e] = to_f32(h[e]);
+            }
+            return;
+        }
+    } else if constexpr (W % 4 == 0) {
+        if (nvalid >= W && (reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+#pragma unroll
+            for (int j = 0; j < W; j += 4) {
+                const uint2 raw = *reinterpret_cast<const uint2*>(p + j);
+                const T16* h = reinterpret_cast<const T16*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) out[j + e] = to_f32(h[e]);
+            }
+            return;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < W; ++j) out[j] = j < nvalid ? to_f32(p[j]) : 0.0f;
+}
+template <int W> __device__ __forceinline__ void ld_row(const __nv_bfloat16* p, int nvalid, float* out) { ld_row16<W>(p, nvalid, out); }
+template <int W> __device__ __forceinline__ void ld_row(const __half* p, int nvalid, float* out) { ld_row16<W>(p, nvalid, out); }
+
+// Strided variant: element j lives at p[j * step]; step 0 broadcasts one value.
+template <int W, typename T>
+__device__ __forceinline__ void ld_row_strided(const T* p, int64_t step, int nvalid, float* out) {
+    if (step == 1) { ld_row<W>(p, nvalid, out); return; }
+    if (step == 0) {
+        const float v = to_f32(p[0]);
+#pragma unroll
+        for (int j = 0; j < W; ++j) out[j] = v;
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < W; ++j) out[j] = j < nvalid ? to_f32(p[j * step]) : 0.0f;
+}
+
+template <int W>
+__device__ __forceinline__ void st_row(float* p, int nvalid, const float* v) {
+    if constexpr (W % 4 == 0) {
+        if (nvalid >= W && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < W; j += 4) *reinterpret_cast<float4*>(p + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            return;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < W; ++j) if (j < nvalid) p[j] = v[j];
+}
+template <int W, typename T16>
+__device__ __forceinline__ void st_row16(T16* p, int nvalid, const float* v) {
+    if constexpr (W % 8 == 0) {
+        if (nvalid >= W && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < W; j += 8) {
+                uint4 raw;
+                T16* h = reinterpret_cast<T16*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) from_f32(h + e, v[j + e]);
+                *reinterpret_cast<uint4*>(p + j) = raw;
+            }
+            return;
+        }
+    } else if constexpr (W % 4 == 0) {
+        if (nvalid >= W && (reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+#pragma unroll
+            for (int j = 0; j < W; j += 4) {
+                uint2 raw;
+                T16* h = reinterpret_cast<T16*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) from_f32(h + e, v[j + e]);
+                *reinterpret_cast<uint2*>(p + j) = raw;
+            }
+            return;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < W; ++j) if (j < nvalid) from_f32(p + j, v[j]);
+}
+template <int W> __device__ __forceinline__ void st_row(__nv_bfloat16* p, int nvalid, const float* v) { st_row16<W>(p, nvalid, v); }
+template <int W> __device__ __forceinline__ void st_row(__half* p, int nvalid, const float* v) { st_row16<W>(p, nvalid, v); }
+
+// Block-wide FP32 sum; the total is valid in thread 0.  All threads of the block must call it.
+__device__ __forceinline__ float block_sum(Ctx& c, float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if (c.lane == 0) c.sh->reduce[c.warp] = v;
+    __syncthreads();
+    float total = 0.0f;
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) total += c.sh->reduce[w];
+    }
+    return total;
+}
+
+// First work item of this block inside a unit whose items start at global position `base`
+// of the stage's concatenated item list (items are dealt round-robin over blocks).
+__device__ __forceinline__ int64_t first_item(int64_t base) {
+    const int64_t g = gridDim.x;
+    int64_t r = (static_cast<int64_t>(blockIdx.x) - base) % g;
+    return r < 0 ? r + g : r;
+}
+
+// Tile rasterisation: groups of kGroupM tile rows are walked column by column so that the
+// blocks of one wave share A rows and B columns in L2.
+constexpr int kGroupM = 16;
+__device__ __forceinline__ void tile_coords(int64_t t, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int64_t per_group = static_cast<int64_t>(kGroupM) * tiles_n;
+    const int group = static_cast<int>(t / per_group);
+    const int first = group * kGroupM;
+    const int rows = min(kGroupM, tiles_m - first);
+    const int within = static_cast<int>(t - static_cast<int64_t>(group) * per_group);
+    tm = first + within % rows;
+    tn = within / rows;
+}
+
+// ----------------------------------------------------------------------------
+// tcgen05 GEMM unit.  C[M,N] = A[M,K] * B[K,N], 16-bit operands, FP32 accumulate in TMEM.
+//   A_MN / B_MN: operand is MN-major in global memory (unit stride along M resp. N)
+//                instead of K-major (unit stride along K).
+//   Epi::run<32>(P, row, col0, nvalid, acc) consumes 32 accumulator columns of one row.
+// Tensor maps: K-major operands use a {64 (K), rows} box; MN-major operands use a
+// {64 (MN), 64 (K)} box issued once per 64-wide MN atom.  Out-of-range parts of a box are
+// zero-filled by TMA, which is what makes M, N and K tails work.
+// ----------------------------------------------------------------------------
+template <int BN, bool A_MN, bool B_MN, int FMT, typename Epi, typename Params>
+__device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorMap* map_a, const CUtensorMap* map_b,
+                                        int M, int N, int K, int64_t item_base) {
+    static_assert(BN % 64 == 0 && BN <= kMaxBN, "BN must be 64, 128, 192 or 256");
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
+    const int kblocks = (K + BK - 1) / BK;
+    const int64_t step = gridDim.x;
+    constexpr uint32_t kBytes = BM * BK * 2 + BN * BK * 2;
+    SharedState* sh = c.sh;
+
+    if (c.warp == 0) {
+        if (c.lane == 0) {
+            for (int64_t t = first_item(item_base); t < tiles && !c.aborted(); t += step) {
+                int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!c.wait(&sh->empty[c.slot], c.slot_phase ^ 1, kErrSmemEmpty)) break;
+                    uint8_t* sa = c.slots + c.slot * kSlotBytes;
+                    uint8_t* sb = sa + kSlotA;
+                    mbar_expect_tx(&sh->full[c.slot], kBytes);
+                    if constexpr (A_MN) {
+#pragma unroll
+                        for (int a = 0; a < BM / 64; ++a) tma_load_2d(sa + a * 8192, map_a, &sh->full[c.slot], tm * BM + a * 64, kb * BK);
+                    } else {
+                        tma_load_2d(sa, map_a, &sh->full[c.slot], kb * BK, tm * BM);
+                    }
+                    if constexpr (B_MN) {
+#pragma unroll
+                        for (int b = 0; b < BN / 64; ++b) tma_load_2d(sb + b * 8192, map_b, &sh->full[c.slot], tn * BN + b * 64, kb * BK);
+                    } else {
+                        tma_load_2d(sb, map_b, &sh->full[c.slot], kb * BK, tn * BN);
+                    }
+                    c.advance_slot();
+                }
+            }
+        }
+        __syncwarp();
+    } else if (c.warp == 1) {
+        if (c.lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(FMT, A_MN ? 1 : 0, B_MN ? 1 : 0, BM, BN);
+            for (int64_t t = first_item(item_base); t < tiles && !c.aborted(); t += step) {
+                if (!c.wait(&sh->tmem_empty[c.acc], c.acc_phase ^ 1, kErrTmemEmpty)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = c.tmem + c.acc * kMaxBN;
+                bool ok = true;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!c.wait(&sh->full[c.slot], c.slot_phase, kErrSmemFull)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(c.slots + c.slot * kSlotBytes);
+                    const uint32_t sb = sa + kSlotA;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t da = A_MN ? umma_desc(sa + k * 2048, 8192, 1024) : umma_desc(sa + k * 32, 16, 1024);
+                        const uint64_t db = B_MN ? umma_desc(sb + k * 2048, 8192, 1024) : umma_desc(sb + k * 32, 16, 1024);
+                        tc_mma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(&sh->empty[c.slot]);     // frees the slot once these MMAs have read it
+                    c.advance_slot();
+                }
+                if (!ok) break;
+                tc_commit(&sh->tmem_full[c.acc]);      // accumulator complete
+                c.advance_acc();
+            }
+        }
+        __syncwarp();
+    } else {
+        const int quarter = c.warp & 3;                // TMEM lanes this warp may read
+        for (int64_t t = first_item(item_base); t < tiles && !c.aborted(); t += step) {
+            int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+            if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
+            tc_fence_after();
+            const int row = tm * BM + quarter * 32 + c.lane;
+            const uint32_t taddr = c.tmem + c.acc * kMaxBN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int cc = 0; cc < BN; cc += 32) {
+                const int col0 = tn * BN + cc;
+                if (col0 >= N) break;                  // warp-uniform
+                float acc[32];
+                tc_ld32(taddr + cc, acc);
+                tc_wait_ld();
+                if (row < M) Epi::template run<32>(P, row, col0, min(32, N - col0), acc);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (c.lane == 0) mbar_arrive(&sh->tmem_empty[c.acc]);
+            c.advance_acc();
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------
+// SIMT GEMM unit (exact FP32 accumulation with fmaf, sequential in K per output).
+// Operands are read through arbitrary element strides and converted to FP32, optionally
+// re-rounded to a 16-bit type first (a cast folded into the load).  32x32 output tile per
+// block-iteration, 128 compute threads each owning a 2x4 strip.
+// ----------------------------------------------------------------------------
+struct SimtSmem { float a[32][33]; float b[32][36]; };
+
+template <typename TA, typename RA, typename TB, typename RB, typename Epi, typename Params>
+__device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm, const TA* A, int64_t a_rs, int64_t a_ks,
+                                          const TB* B, int64_t b_ks, int64_t b_cs, int M, int N, int K, int64_t item_base) {
+    const int tiles_n = (N + 31) / 32;
+    const int64_t tiles = static_cast<int64_t>((M + 31) / 32) * tiles_n;
+    const int tid = threadIdx.x;
+    const int ty = tid / 8, tx = tid % 8;      // valid for tid < 128: rows 2*ty.., cols 4*tx..
+    for (int64_t t = first_item(item_base); t < tiles; t += gridDim.x) {
+        const int row0 = static_cast<int>(t / tiles_n) * 32, col0 = static_cast<int>(t % tiles_n) * 32;
+        float acc[2][4] = {};
+        for (int k0 = 0; k0 < K; k0 += 32) {
+            __syncthreads();
+            for (int p = tid; p < 1024; p += kThreads) {
+                // A tile: consecutive threads walk K when K is the unit-stride axis, rows otherwise.
+                int ar, ak;
+                if (a_ks <= a_rs) { ar = p / 32; ak = p % 32; } else { ar = p % 32; ak = p / 32; }
+                const int gr = row0 + ar, gk = k0 + ak;
+                sm->a[ar][ak] = (gr < M && gk < K) ? RA::rnd(to_f32(A[gr * a_rs + gk * a_ks])) : 0.0f;
+                int bk, bc;
+                if (b_cs <= b_ks) { bk = p / 32; bc = p % 32; } else { bk = p % 32; bc = p / 32; }
+                const int gk2 = k0 + bk, gc = col0 + bc;
+                sm->b[bk][bc] = (gk2 < K && gc < N) ? RB::rnd(to_f32(B[gk2 * b_ks + gc * b_cs])) : 0.0f;
+            }
+            __syncthreads();
+            if (tid < 128) {
+#pragma unroll 8
+                for (int k = 0; k < 32; ++k) {
+                    const float a0 = sm->a[2 * ty][k], a1 = sm->a[2 * ty + 1][k];
+                    const float4 b = *reinterpret_cast<const float4*>(&sm->b[k][4 * tx]);
+                    acc[0][0] = fmaf(a0, b.x, acc[0][0]); acc[0][1] = fmaf(a0, b.y, acc[0][1]);
+                    acc[0][2] = fmaf(a0, b.z, acc[0][2]); acc[0][3] = fmaf(a0, b.w, acc[0][3]);
+                    acc[1][0] = fmaf(a1, b.x, acc[1][0]); acc[1][1] = fmaf(a1, b.y, acc[1][1]);
+                    acc[1][2] = fmaf(a1, b.z, acc[1][2]); acc[1][3] = fmaf(a1, b.w, acc[1][3]);
+                }
+            }
+        }
+        if (tid < 128) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = row0 + 2 * ty + i, cc = col0 + 4 * tx;
+                if (r < M && cc < N) Epi::template run<4>(P, r, cc, min(4, N - cc), acc[i]);
+            }
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------
+// GEMV unit (M == 1): y[n] = sum_k a[k] * B[k, n], FP32 accumulation.  Operands may be
+// stored in a wider type and rounded on load (RA / RB), which folds an FP32 -> BF16 cast of a
+// master weight into the read.  128-bit loads, warp-shuffle reductions.
+//   B_KMAJOR: B has unit stride along K (a transposed weight view): one warp per output
+//             column, each lane takes 8 consecutive K elements per step.
+//   otherwise B has unit stride along N: lane%8 owns 8 consecutive columns, lane/8 strides K
+//             by 4; partial sums of the 4 K groups are combined with two shuffles.
+// ----------------------------------------------------------------------------
+template <typename TA, typename RA, typename TB, typename RB, bool B_KMAJOR, typename Epi, typename Params>
+__device__ __forceinline__ void gemv(Ctx& c, const Params& P, const TA* a, int64_t a_ks, const TB* B, int64_t b_ld,
+                                     int N, int K, int64_t item_base) {
+    constexpr int kWarps = kThreads / 32;
+    if constexpr (B_KMAJOR) {
+        const int64_t items = (N + kWarps - 1) / kWarps;
+        for (int64_t it = first_item(item_base); it < items; it += gridDim.x) {
+            const int n = static_cast<int>(it) * kWarps + c.warp;
+            float acc = 0.0f;
+            if (n < N) {
+                const TB* col = B + static_cast<int64_t>(n) * b_ld;
+                for (int k = c.lane * 8; k < K; k += 256) {
+                    const int nvalid = min(8, K - k);
+                    float av[8], bv[8];
+                    ld_row_strided<8>(a + static_cast<int64_t>(k) * a_ks, a_ks, nvalid, av);
+                    ld_row<8>(col + k, nvalid, bv);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc = fmaf(RA::rnd(av[e]), RB::rnd(bv[e]), acc);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (n < N && c.lane == 0) Epi::template run<1>(P, 0, n, 1, &acc);
+        }
+    } else {
+        const int64_t items = (N + 64 * kWarps - 1) / (64 * kWarps);
+        for (int64_t it = first_item(item_base); it < items; it += gridDim.x) {
+            const int n0 = (static_cast<int>(it) * kWarps + c.warp) * 64 + (c.lane & 7) * 8;
+            float acc[8] = {};
+            if (n0 < N) {
+                const int nvalid = min(8, N - n0);
+                for (int k = c.lane >> 3; k < K; k += 4) {
+                    float b[8];
+                    ld_row<8>(B + static_cast<int64_t>(k) * b_ld + n0, nvalid, b);
+                    const float av = RA::rnd(to_f32(a[static_cast<int64_t>(k) * a_ks]));
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] = fmaf(av, RB::rnd(b[e]), acc[e]);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 8);
+                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
+            }
+            if (n0 < N && c.lane < 8) Epi::template run<8>(P, 0, n0, min(8, N - n0), acc);
+        }
+    }
+}
+
+}  // namespace tk

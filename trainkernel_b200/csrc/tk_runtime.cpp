@@ -1,0 +1,312 @@
+// libtrainkernel_rt.so: C ABI over the CUDA driver API (see include/trainkernel_rt.h).
+//
+// The driver library is opened with dlopen on first use, so this file links
+// against nothing but libdl and can be loaded on a machine without a GPU.
+#include "trainkernel_rt.h"
+
+#include <cuda.h>
+#include <dlfcn.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+namespace {
+
+thread_local char g_error[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char* format, ...) {
+    va_list args;
+    va_start(args, format);
+    vsnprintf(g_error, sizeof(g_error), format, args);
+    va_end(args);
+    return code;
+}
+
+#define TK_STR2(x) #x
+#define TK_STR(x) TK_STR2(x)
+#define TK_DRIVER_SYMBOLS(X)                                                                        \
+    X(cuInit) X(cuDeviceGet) X(cuDeviceGetAttribute) X(cuDevicePrimaryCtxRetain)                    \
+    X(cuDevicePrimaryCtxRelease) X(cuCtxPushCurrent) X(cuCtxPopCurrent) X(cuCtxSynchronize)         \
+    X(cuModuleLoadData) X(cuModuleUnload) X(cuModuleGetFunction) X(cuFuncSetAttribute)              \
+    X(cuFuncGetAttribute) X(cuOccupancyMaxActiveBlocksPerMultiprocessor) X(cuLaunchKernelEx)        \
+    X(cuMemAlloc) X(cuMemFree) X(cuMemsetD8) X(cuMemcpyDtoH) X(cuStreamSynchronize)                 \
+    X(cuTensorMapEncodeTiled) X(cuGetErrorString)
+
+struct Driver {
+#define X(sym) decltype(&sym) sym##_ = nullptr;
+    TK_DRIVER_SYMBOLS(X)
+#undef X
+    bool ready = false;
+};
+
+Driver g_driver;
+std::once_flag g_driver_once;
+char g_driver_error[256] = "";
+
+void load_driver() {
+    void* lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+    if (!lib) {
+        snprintf(g_driver_error, sizeof(g_driver_error), "cannot open libcuda.so.1: %s", dlerror());
+        return;
+    }
+#define X(sym)                                                                                      \
+    g_driver.sym##_ = reinterpret_cast<decltype(&sym)>(dlsym(lib, TK_STR(sym)));                    \
+    if (!g_driver.sym##_) {                                                                         \
+        snprintf(g_driver_error, sizeof(g_driver_error), "libcuda.so.1 lacks %s", TK_STR(sym));     \
+        return;                                                                                     \
+    }
+    TK_DRIVER_SYMBOLS(X)
+#undef X
+    if (g_driver.cuInit_(0) != CUDA_SUCCESS) {
+        snprintf(g_driver_error, sizeof(g_driver_error), "cuInit failed");
+        return;
+    }
+    g_driver.ready = true;
+}
+
+int driver() {
+    std::call_once(g_driver_once, load_driver);
+    return g_driver.ready ? 0 : fail(TK_E_DRIVER, "trainkernel: %s", g_driver_error);
+}
+
+int check(CUresult result, const char* what) {
+    if (result == CUDA_SUCCESS) return 0;
+    const char* text = nullptr;
+    g_driver.cuGetErrorString_(result, &text);
+    return fail(static_cast<int>(result), "trainkernel: %s failed: %s", what, text ? text : "unknown CUDA error");
+}
+
+constexpr int kSyncSlots = 64;        // one {count, generation} pair per 128-byte line
+constexpr int kSyncStride = 128;
+constexpr int kStampCount = 64;
+
+struct ContextScope {
+    bool pushed = false;
+    explicit ContextScope(CUcontext context) { pushed = g_driver.cuCtxPushCurrent_(context) == CUDA_SUCCESS; }
+    ~ContextScope() {
+        CUcontext ignored;
+        if (pushed) g_driver.cuCtxPopCurrent_(&ignored);
+    }
+};
+
+}  // namespace
+
+struct tk_module {
+    CUdevice device = 0;
+    CUcontext context = nullptr;
+    CUmodule module = nullptr;
+    CUfunction function = nullptr;
+    int threads = 0;
+    size_t dynamic_smem = 0;
+    int n_inputs = 0, n_outputs = 0;
+    int slots_in = 1, slots_out = 1, slots_maps = 1;
+    std::vector<tk_tensor_map_desc> maps;
+    CUdeviceptr state = 0;            // sync slots | status words | stage stamps
+    std::atomic<uint32_t> next_slot{0};
+    std::atomic<uint64_t> timeout_ns{2000000000ull};
+    std::atomic<uint32_t> arrivals{0};
+    int sm_count = 0;
+    int blocks_per_sm = 0;
+    size_t param_bytes = 0;
+
+    CUdeviceptr sync_slot(uint32_t i) const { return state + static_cast<size_t>(i) * kSyncStride; }
+    CUdeviceptr status() const { return state + static_cast<size_t>(kSyncSlots) * kSyncStride; }
+    CUdeviceptr stamps() const { return status() + 128; }
+    size_t state_bytes() const { return static_cast<size_t>(kSyncSlots) * kSyncStride + 128 + kStampCount * 8; }
+};
+
+extern "C" {
+
+const char* tk_last_error(void) { return g_error; }
+
+uint64_t tk_launch_count(void) { return g_launches.load(); }
+
+int tk_module_load(const void* cubin, size_t cubin_bytes, const char* entry, int device, int threads,
+                   size_t dynamic_smem, int n_inputs, int n_outputs, const tk_tensor_map_desc* maps,
+                   int n_maps, tk_module** out) {
+    if (!cubin || !cubin_bytes || !entry || !out || threads <= 0 || n_inputs < 0 || n_outputs < 0 || n_maps < 0 ||
+        (n_maps > 0 && !maps))
+        return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_load");
+    if (int rc = driver()) return rc;
+    tk_module* m = new tk_module();
+    m->threads = threads;
+    m->dynamic_smem = dynamic_smem;
+    m->n_inputs = n_inputs;
+    m->n_outputs = n_outputs;
+    m->slots_in = n_inputs > 0 ? n_inputs : 1;
+    m->slots_out = n_outputs > 0 ? n_outputs : 1;
+    m->slots_maps = n_maps > 0 ? n_maps : 1;
+    m->maps.assign(maps, maps + n_maps);
+    m->param_bytes = 128 * static_cast<size_t>(m->slots_maps) + 8 * static_cast<size_t>(m->slots_in + m->slots_out) + 8 * 6;
+    int rc = 0;
+    do {
+        if ((rc = check(g_driver.cuDeviceGet_(&m->device, device), "cuDeviceGet"))) break;
+        if ((rc = check(g_driver.cuDevicePrimaryCtxRetain_(&m->context, m->device), "cuDevicePrimaryCtxRetain"))) break;
+        ContextScope scope(m->context);
+        if ((rc = check(g_driver.cuModuleLoadData_(&m->module, cubin), "cuModuleLoadData"))) break;
+        if ((rc = check(g_driver.cuModuleGetFunction_(&m->function, m->module, entry), "cuModuleGetFunction"))) break;
+        if (dynamic_smem > 0 &&
+            (rc = check(g_driver.cuFuncSetAttribute_(m->function, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
+                                                     static_cast<int>(dynamic_smem)), "cuFuncSetAttribute(dynamic shared memory)")))
+            break;
+        if ((rc = check(g_driver.cuDeviceGetAttribute_(&m->sm_count, CU_DEVICE_ATTRIBUTE_MULTIPROCESSOR_COUNT, m->device), "cuDeviceGetAttribute"))) break;
+        if ((rc = check(g_driver.cuOccupancyMaxActiveBlocksPerMultiprocessor_(&m->blocks_per_sm, m->function, threads, dynamic_smem),
+                        "cuOccupancyMaxActiveBlocksPerMultiprocessor")))
+            break;
+        if (m->blocks_per_sm < 1) { rc = fail(TK_E_CAPACITY, "trainkernel: kernel has no resident blocks"); break; }
+        if ((rc = check(g_driver.cuMemAlloc_(&m->state, m->state_bytes()), "cuMemAlloc(kernel state)"))) break;
+        if ((rc = check(g_driver.cuMemsetD8_(m->state, 0, m->state_bytes()), "cuMemsetD8(kernel state)"))) break;
+    } while (false);
+    if (rc) {
+        char saved[sizeof(g_error)];
+        memcpy(saved, g_error, sizeof(saved));
+        tk_module_unload(m);
+        memcpy(g_error, saved, sizeof(saved));
+        return rc;
+    }
+    *out = m;
+    return 0;
+}
+
+void tk_module_unload(tk_module* m) {
+    if (!m) return;
+    if (m->context) {
+        {
+            ContextScope scope(m->context);
+            if (m->state) g_driver.cuMemFree_(m->state);
+            if (m->module) g_driver.cuModuleUnload_(m->module);
+        }
+        g_driver.cuDevicePrimaryCtxRelease_(m->device);
+    }
+    delete m;
+}
+
+int tk_module_launch(tk_module* m, const void* const* inputs, void* const* outputs, void* workspace, int grid, void* stream) {
+    if (!m || grid < 1 || (m->n_inputs > 0 && !inputs) || (m->n_outputs > 0 && !outputs))
+        return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_launch");
+    if (grid > m->sm_count * m->blocks_per_sm)
+        return fail(TK_E_CAPACITY, "trainkernel: grid %d exceeds the %d co-resident blocks a cooperative launch allows", grid,
+                    m->sm_count * m->blocks_per_sm);
+    // Kernel parameter block: tensor maps, input pointers, output pointers, then the scalars.
+    alignas(64) unsigned char block[4096];
+    if (m->param_bytes > sizeof(block)) return fail(TK_E_ARGUMENT, "trainkernel: parameter block too large");
+    memset(block, 0, m->param_bytes);
+    for (size_t i = 0; i < m->maps.size(); ++i) {
+        const tk_tensor_map_desc& d = m->maps[i];
+        const unsigned char* base = nullptr;
+        if (d.base_kind == TK_BASE_INPUT && d.base_index >= 0 && d.base_index < m->n_inputs) base = static_cast<const unsigned char*>(inputs[d.base_index]);
+        else if (d.base_kind == TK_BASE_OUTPUT && d.base_index >= 0 && d.base_index < m->n_outputs) base = static_cast<const unsigned char*>(outputs[d.base_index]);
+        else if (d.base_kind == TK_BASE_WORKSPACE) base = static_cast<const unsigned char*>(workspace);
+        if (!base) return fail(TK_E_ARGUMENT, "trainkernel: tensor map %zu has no base pointer", i);
+        base += d.byte_offset;
+        if (reinterpret_cast<uintptr_t>(base) & 15)
+            return fail(TK_E_ARGUMENT, "trainkernel: tensor-core operand %zu is not 16-byte aligned", i);
+        cuuint64_t dims[2] = {d.inner, d.outer};
+        cuuint64_t strides[1] = {d.outer_stride_bytes};
+        cuuint32_t box[2] = {d.box_inner, d.box_outer};
+        cuuint32_t element_strides[2] = {1, 1};
+        CUresult result = g_driver.cuTensorMapEncodeTiled_(
+            reinterpret_cast<CUtensorMap*>(block + 128 * i), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+            const_cast<unsigned char*>(base), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (int rc = check(result, "cuTensorMapEncodeTiled")) return rc;
+    }
+    unsigned char* cursor = block + 128 * static_cast<size_t>(m->slots_maps);
+    for (int i = 0; i < m->n_inputs; ++i) memcpy(cursor + 8 * i, &inputs[i], 8);
+    cursor += 8 * static_cast<size_t>(m->slots_in);
+    for (int i = 0; i < m->n_outputs; ++i) memcpy(cursor + 8 * i, &outputs[i], 8);
+    cursor += 8 * static_cast<size_t>(m->slots_out);
+    const uint32_t slot = m->next_slot.fetch_add(1) % kSyncSlots;
+    const CUdeviceptr sync = m->sync_slot(slot), status = m->status(), stamps = m->stamps();
+    const uint64_t timeout = m->timeout_ns.load();
+    const uint32_t arrivals = m->arrivals.load();
+    memcpy(cursor, &workspace, 8);
+    memcpy(cursor + 8, &sync, 8);
+    memcpy(cursor + 16, &status, 8);
+    memcpy(cursor + 24, &stamps, 8);
+    memcpy(cursor + 32, &timeout, 8);
+    memcpy(cursor + 40, &arrivals, 4);
+
+    ContextScope scope(m->context);
+    CUlaunchAttribute attribute;
+    memset(&attribute, 0, sizeof(attribute));
+    attribute.id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE;
+    attribute.value.cooperative = 1;
+    CUlaunchConfig config;
+    memset(&config, 0, sizeof(config));
+    config.gridDimX = static_cast<unsigned>(grid);
+    config.gridDimY = config.gridDimZ = 1;
+    config.blockDimX = static_cast<unsigned>(m->threads);
+    config.blockDimY = config.blockDimZ = 1;
+    config.sharedMemBytes = static_cast<unsigned>(m->dynamic_smem);
+    config.hStream = static_cast<CUstream>(stream);
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    void* params[1] = {block};
+    if (int rc = check(g_driver.cuLaunchKernelEx_(&config, m->function, params, nullptr), "cuLaunchKernelEx")) return rc;
+    g_launches.fetch_add(1);
+    return 0;
+}
+
+int tk_module_resource_usage(tk_module* m, int64_t out[4]) {
+    if (!m || !out) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_resource_usage");
+    ContextScope scope(m->context);
+    int regs = 0, local = 0, shared = 0;
+    if (int rc = check(g_driver.cuFuncGetAttribute_(&regs, CU_FUNC_ATTRIBUTE_NUM_REGS, m->function), "cuFuncGetAttribute")) return rc;
+    if (int rc = check(g_driver.cuFuncGetAttribute_(&local, CU_FUNC_ATTRIBUTE_LOCAL_SIZE_BYTES, m->function), "cuFuncGetAttribute")) return rc;
+    if (int rc = check(g_driver.cuFuncGetAttribute_(&shared, CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES, m->function), "cuFuncGetAttribute")) return rc;
+    out[0] = regs;
+    out[1] = local;
+    out[2] = static_cast<int64_t>(shared) + static_cast<int64_t>(m->dynamic_smem);
+    out[3] = m->blocks_per_sm;
+    return 0;
+}
+
+int tk_module_max_coresident_blocks(tk_module* m, int* out) {
+    if (!m || !out) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_max_coresident_blocks");
+    *out = m->sm_count * m->blocks_per_sm;
+    return 0;
+}
+
+int tk_module_status(tk_module* m, void* stream, uint32_t out[4]) {
+    if (!m || !out) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_status");
+    ContextScope scope(m->context);
+    if (int rc = check(g_driver.cuStreamSynchronize_(static_cast<CUstream>(stream)), "cuStreamSynchronize")) return rc;
+    if (int rc = check(g_driver.cuMemcpyDtoH_(out, m->status(), 16), "cuMemcpyDtoH(status)")) return rc;
+    if (out[0] != 0)
+        return fail(TK_E_KERNEL, "trainkernel: kernel wait timed out (code %u, stage %u, block %u, detail %u)", out[0], out[1], out[2], out[3]);
+    return 0;
+}
+
+int tk_module_reset(tk_module* m) {
+    if (!m) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_reset");
+    ContextScope scope(m->context);
+    if (int rc = check(g_driver.cuCtxSynchronize_(), "cuCtxSynchronize")) return rc;
+    return check(g_driver.cuMemsetD8_(m->state, 0, m->state_bytes()), "cuMemsetD8(kernel state)");
+}
+
+int tk_module_set_timeout(tk_module* m, uint64_t nanoseconds) {
+    if (!m || nanoseconds == 0) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_set_timeout");
+    m->timeout_ns.store(nanoseconds);
+    return 0;
+}
+
+int tk_module_set_expected_arrivals(tk_module* m, uint32_t arrivals) {
+    if (!m) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_set_expected_arrivals");
+    m->arrivals.store(arrivals);
+    return 0;
+}
+
+int tk_module_stage_stamps(tk_module* m, void* stream, uint64_t* out, int count) {
+    if (!m || !out || count < 0 || count > kStampCount) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_stage_stamps");
+    ContextScope scope(m->context);
+    if (int rc = check(g_driver.cuStreamSynchronize_(static_cast<CUstream>(stream)), "cuStreamSynchronize")) return rc;
+    return check(g_driver.cuMemcpyDtoH_(out, m->stamps(), static_cast<size_t>(count) * 8), "cuMemcpyDtoH(stamps)");
+}
+
+}  // extern "C"

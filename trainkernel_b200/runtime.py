@@ -1,0 +1,348 @@
+"""Build, load and launch generated kernels through the C-ABI runtime shim.
+
+Keeps the reference's Python surface — `compile_program`, `CompiledProgram`
+(`__call__`, `allocate`, `run_into`, `resource_usage`, `_validate_inputs`) and
+`ExecutionBuffers` (reference: trainkernel/runtime.py:16-161) — with a
+different mechanism underneath: the generated source is compiled by `nvcc`
+straight to an sm_100a cubin (no PyTorch or pybind11 headers), cached on disk by
+content hash, and loaded and launched by `libtrainkernel_rt.so` (CUDA driver
+API, `include/trainkernel_rt.h`) on PyTorch's current stream.  PyTorch is used
+for tensors and streams only.  There is no CPU or eager fallback: without the
+shim, nvcc or an sm_100 device this module raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import tempfile
+import threading
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Any
+
+import torch
+from torch.utils._pytree import tree_flatten
+
+from .codegen import GeneratedKernel, generate
+from .ir import Program
+
+PACKAGE_DIR = Path(__file__).resolve().parent
+CSRC_DIR = PACKAGE_DIR / "csrc"
+INCLUDE_DIR = PACKAGE_DIR.parent / "include"
+LIBRARY_PATH = PACKAGE_DIR / "libtrainkernel_rt.so"
+CACHE_DIR = Path(os.environ.get("TRAINKERNEL_CACHE", PACKAGE_DIR / "_cache"))
+NVCC_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "--fmad=false", "-lineinfo")
+
+_BASE_KIND = {"in": 0, "out": 1, "ws": 2}
+_lock = threading.Lock()
+_library: ctypes.CDLL | None = None
+
+
+class TensorMapDesc(ctypes.Structure):
+    _fields_ = [
+        ("base_kind", ctypes.c_int32), ("base_index", ctypes.c_int32), ("byte_offset", ctypes.c_uint64),
+        ("inner", ctypes.c_uint64), ("outer", ctypes.c_uint64), ("outer_stride_bytes", ctypes.c_uint64),
+        ("box_inner", ctypes.c_uint32), ("box_outer", ctypes.c_uint32), ("element_bytes", ctypes.c_uint32),
+        ("reserved", ctypes.c_uint32),
+    ]
+
+
+def _cuda_home() -> str | None:
+    for candidate in (os.environ.get("CUDA_HOME"), os.environ.get("CUDA_PATH"), "/usr/local/cuda"):
+        if candidate and (Path(candidate) / "bin" / "nvcc").exists():
+            return candidate
+    found = shutil.which("nvcc")
+    return str(Path(found).resolve().parents[1]) if found else None
+
+
+def build_library(force: bool = False) -> Path:
+    """Compile `csrc/tk_runtime.cpp` into `libtrainkernel_rt.so` next to this file."""
+    source = CSRC_DIR / "tk_runtime.cpp"
+    header = INCLUDE_DIR / "trainkernel_rt.h"
+    fresh = LIBRARY_PATH.exists() and LIBRARY_PATH.stat().st_mtime >= max(source.stat().st_mtime, header.stat().st_mtime)
+    if fresh and not force:
+        return LIBRARY_PATH
+    cuda = _cuda_home()
+    if cuda is None:
+        raise RuntimeError("trainkernel: CUDA toolkit headers are required to build the runtime shim")
+    command = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-I", str(INCLUDE_DIR), "-I", str(Path(cuda) / "include"),
+               "-o", str(LIBRARY_PATH), str(source), "-ldl", "-lpthread"]
+    done = subprocess.run(command, capture_output=True, text=True)
+    if done.returncode != 0:
+        raise RuntimeError(f"trainkernel: building the runtime shim failed:\n{done.stderr}")
+    return LIBRARY_PATH
+
+
+def library() -> ctypes.CDLL:
+    """The loaded shim with argument types declared; built on first use if missing."""
+    global _library
+    with _lock:
+        if _library is not None:
+            return _library
+        path = build_library()
+        lib = ctypes.CDLL(str(path))
+        p, u64, u32, i32 = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int
+        lib.tk_last_error.restype = ctypes.c_char_p
+        lib.tk_launch_count.restype = u64
+        lib.tk_module_load.argtypes = [p, ctypes.c_size_t, ctypes.c_char_p, i32, i32, ctypes.c_size_t, i32, i32,
+                                       ctypes.POINTER(TensorMapDesc), i32, ctypes.POINTER(p)]
+        lib.tk_module_launch.argtypes = [p, ctypes.POINTER(p), ctypes.POINTER(p), p, i32, p]
+        lib.tk_module_resource_usage.argtypes = [p, ctypes.POINTER(ctypes.c_int64)]
+        lib.tk_module_max_coresident_blocks.argtypes = [p, ctypes.POINTER(i32)]
+        lib.tk_module_status.argtypes = [p, p, ctypes.POINTER(u32)]
+        lib.tk_module_reset.argtypes = [p]
+        lib.tk_module_set_timeout.argtypes = [p, u64]
+        lib.tk_module_set_expected_arrivals.argtypes = [p, u32]
+        lib.tk_module_stage_stamps.argtypes = [p, p, ctypes.POINTER(u64), i32]
+        lib.tk_module_unload.argtypes = [p]
+        lib.tk_module_unload.restype = None
+        _library = lib
+        return lib
+
+
+def _raise(code: int) -> None:
+    message = library().tk_last_error().decode() or f"trainkernel: runtime shim error {code}"
+    raise RuntimeError(message)
+
+
+def build_cubin(source: str, *, verbose: bool = False) -> bytes:
+    """nvcc-compile generated source to an sm_100a cubin; cached by content hash."""
+    header = (CSRC_DIR / "tk_device.cuh").read_bytes()
+    digest = hashlib.sha256(source.encode() + b"\0" + header + b"\0" + " ".join(NVCC_FLAGS).encode()).hexdigest()[:32]
+    cached = CACHE_DIR / f"{digest}.cubin"
+    if cached.exists():
+        return cached.read_bytes()
+    cuda = _cuda_home()
+    if cuda is None:
+        raise RuntimeError("trainkernel: CUDA toolkit with nvcc is required to compile generated kernels")
+    CACHE_DIR.mkdir(parents=True, exist_ok=True)
+    with tempfile.TemporaryDirectory(prefix="trainkernel_") as work:
+        unit = Path(work) / "kernel.cu"
+        unit.write_text(source)
+        target = Path(work) / "kernel.cubin"
+        command = [str(Path(cuda) / "bin" / "nvcc"), *NVCC_FLAGS, "-I", str(CSRC_DIR), "-cubin", "-o", str(target), str(unit)]
+        if verbose:
+            command.insert(1, "-Xptxas=-v")
+        done = subprocess.run(command, capture_output=True, text=True)
+        if verbose:
+            print(done.stderr)
+        if done.returncode != 0:
+            raise RuntimeError(f"trainkernel: nvcc failed on the generated kernel:\n{done.stderr[-4000:]}")
+        data = target.read_bytes()
+    scratch = cached.with_suffix(f".tmp{os.getpid()}")
+    scratch.write_bytes(data)
+    os.replace(scratch, cached)
+    return data
+
+
+@dataclass
+class ExecutionBuffers:
+    """Caller-owned output and workspace storage for one launch.
+
+    Reusing the same buffers for a second launch is only valid when the caller
+    orders it after the first on the stream.
+    """
+
+    outputs: tuple[torch.Tensor, ...]
+    workspace: torch.Tensor
+
+
+class _Module:
+    """Owner of one `tk_module*`."""
+
+    def __init__(self, generated: GeneratedKernel, cubin: bytes, device: torch.device):
+        lib = library()
+        maps = (TensorMapDesc * max(1, len(generated.tensor_maps)))()
+        for i, spec in enumerate(generated.tensor_maps):
+            kind, where = spec.base
+            maps[i] = TensorMapDesc(_BASE_KIND[kind], 0 if kind == "ws" else where,
+                                    spec.byte_offset + (where if kind == "ws" else 0), spec.inner, spec.outer,
+                                    spec.outer_stride_bytes, spec.box_inner, spec.box_outer, 2, 0)
+        handle = ctypes.c_void_p()
+        self._cubin = ctypes.create_string_buffer(cubin, len(cubin))
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        code = lib.tk_module_load(self._cubin, len(cubin), generated.entry.encode(), index, generated.threads,
+                                  generated.dynamic_smem, generated.input_count, generated.output_count,
+                                  maps, len(generated.tensor_maps), ctypes.byref(handle))
+        if code:
+            _raise(code)
+        self.handle = handle
+        self.lib = lib
+        limit = ctypes.c_int()
+        if lib.tk_module_max_coresident_blocks(handle, ctypes.byref(limit)):
+            _raise(1)
+        self.grid = max(1, min(generated.grid, limit.value))
+        self.n_in = max(1, generated.input_count)
+        self.n_out = max(1, generated.output_count)
+
+    def launch(self, inputs, outputs, workspace: torch.Tensor, stream: int) -> None:
+        ins = (ctypes.c_void_p * self.n_in)(*[t.data_ptr() for t in inputs])
+        outs = (ctypes.c_void_p * self.n_out)(*[t.data_ptr() for t in outputs])
+        code = self.lib.tk_module_launch(self.handle, ins, outs, workspace.data_ptr(), self.grid, stream)
+        if code:
+            _raise(code)
+
+    def __del__(self):
+        handle, self.handle = getattr(self, "handle", None), None
+        if handle:
+            try:
+                self.lib.tk_module_unload(handle)
+            except Exception:
+                pass
+
+
+class CompiledProgram:
+    """One specialised kernel plus the argument checks that guard its launch.
+
+    Every call allocates fresh outputs and workspace unless the caller passes
+    its own `ExecutionBuffers`.  Results carry no autograd history; gradients
+    come from differentiation inside the compiled function.
+    """
+
+    def __init__(self, program: Program, generated: GeneratedKernel, module: Any, device: torch.device,
+                 inplace_outputs: dict[int, int] | None = None):
+        self.program = program
+        self.generated = generated
+        self.source = generated.source
+        self.module = module
+        self.device = device
+        self.inplace_outputs = dict(inplace_outputs or {})
+
+    # -- introspection -------------------------------------------------------------
+    def resource_usage(self) -> dict[str, int]:
+        """Compiler-reported resources of the kernel (no hardware counters involved)."""
+        values = (ctypes.c_int64 * 4)()
+        code = self.module.lib.tk_module_resource_usage(self.module.handle, values)
+        if code:
+            _raise(code)
+        names = ("registers_per_thread", "local_bytes_per_thread", "shared_bytes_per_block", "resident_blocks_per_sm")
+        return dict(zip(names, (int(v) for v in values)))
+
+    def status(self) -> tuple[int, int, int, int]:
+        """Synchronise the current stream and return the kernel's status words; raises on a timed-out wait."""
+        words = (ctypes.c_uint32 * 4)()
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        code = self.module.lib.tk_module_status(self.module.handle, stream, words)
+        if code:
+            _raise(code)
+        return tuple(int(w) for w in words)
+
+    def stage_stamps(self) -> list[int]:
+        """Per-stage %globaltimer values of the last launch (kernel generated with `stage_stamps=True`)."""
+        count = self.generated.stages + 1
+        stamps = (ctypes.c_uint64 * count)()
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        code = self.module.lib.tk_module_stage_stamps(self.module.handle, stream, stamps, count)
+        if code:
+            _raise(code)
+        return [int(s) for s in stamps]
+
+    # -- argument checks -------------------------------------------------------------
+    def _validate_inputs(self, inputs: tuple[torch.Tensor, ...]) -> None:
+        expected = self.program.inputs
+        if len(inputs) != len(expected):
+            raise ValueError(f"trainkernel: expected {len(expected)} inputs, got {len(inputs)}")
+        for position, (tensor, spec) in enumerate(zip(inputs, expected)):
+            if not isinstance(tensor, torch.Tensor):
+                raise TypeError(f"trainkernel: input {position} must be a tensor")
+            if tensor.is_neg() or tensor.is_conj():
+                raise ValueError("trainkernel: resolve lazy negative or conjugate input views before execution")
+            same = (tensor.device == self.device and tuple(tensor.shape) == spec.shape
+                    and tuple(tensor.stride()) == spec.strides and tensor.dtype == getattr(torch, spec.dtype))
+            if not same:
+                raise ValueError(f"trainkernel: input {position} does not match compiled device, shape, stride, or dtype")
+        for target in self.inplace_outputs.values():
+            if inputs[target].requires_grad:
+                raise ValueError("trainkernel: inplace targets must be detached from autograd")
+
+    def allocate(self, *inputs: torch.Tensor) -> ExecutionBuffers:
+        if self.inplace_outputs:
+            self._validate_inputs(inputs)
+        outputs = []
+        for slot, spec in enumerate(self.program.outputs):
+            if slot in self.inplace_outputs:
+                outputs.append(inputs[self.inplace_outputs[slot]])
+            else:
+                outputs.append(torch.empty(spec.shape, dtype=getattr(torch, spec.dtype), device=self.device))
+        workspace = torch.empty(self.generated.workspace_elements, dtype=torch.float32, device=self.device)
+        return ExecutionBuffers(tuple(outputs), workspace)
+
+    def _check_buffers(self, inputs: tuple[torch.Tensor, ...], buffers: ExecutionBuffers) -> None:
+        outputs, workspace = buffers.outputs, buffers.workspace
+        if len(outputs) != len(self.program.outputs):
+            raise ValueError("trainkernel: incorrect output buffer count")
+        if (workspace.device != self.device or workspace.dtype != torch.float32 or not workspace.is_contiguous()
+                or workspace.numel() < self.generated.workspace_elements):
+            raise ValueError("trainkernel: workspace does not match compiled requirements")
+        # Storage-level disjointness: conservative, but a write can then never clobber something still to be read.
+        written: list[int] = []
+        shared_with_inputs: set[int] = set()
+        for slot, (tensor, spec) in enumerate(zip(outputs, self.program.outputs)):
+            fits = (tensor.device == self.device and tensor.dtype == getattr(torch, spec.dtype)
+                    and tuple(tensor.shape) == spec.shape and tensor.is_contiguous())
+            if not fits:
+                raise ValueError("trainkernel: output buffer does not match compiled requirements")
+            if tensor.numel():
+                written.append(tensor.untyped_storage().data_ptr())
+            if slot not in self.inplace_outputs:
+                continue
+            index = self.inplace_outputs[slot]
+            target = inputs[index]
+            if tensor.data_ptr() != target.data_ptr() or tuple(tensor.stride()) != tuple(target.stride()):
+                raise ValueError("trainkernel: inplace output must bind its declared input")
+            if target.numel():
+                storage = target.untyped_storage().data_ptr()
+                for other, value in enumerate(inputs):
+                    if other != index and value.numel() and value.untyped_storage().data_ptr() == storage:
+                        raise ValueError("trainkernel: inplace target must not alias another input")
+                shared_with_inputs.add(storage)
+        if workspace.numel():
+            written.append(workspace.untyped_storage().data_ptr())
+        read = {tensor.untyped_storage().data_ptr() for tensor in inputs if tensor.numel()}
+        if len(set(written)) != len(written) or (read & set(written)) - shared_with_inputs:
+            raise ValueError("trainkernel: execution buffers must not alias inputs or each other")
+
+    # -- execution -------------------------------------------------------------------
+    def run_into(self, *inputs: torch.Tensor, buffers: ExecutionBuffers) -> tuple[torch.Tensor, ...]:
+        self._validate_inputs(inputs)
+        self._check_buffers(inputs, buffers)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self.module.launch(inputs, buffers.outputs, buffers.workspace, stream)
+        if self.inplace_outputs:
+            torch.autograd.graph.increment_version([inputs[i] for i in self.inplace_outputs.values()])
+        return buffers.outputs
+
+    def __call__(self, *inputs: torch.Tensor) -> tuple[torch.Tensor, ...]:
+        return self.run_into(*inputs, buffers=self.allocate(*inputs))
+
+
+def compile_program(program: Program, example_inputs: tuple[Any, ...] | list[Any], *,
+                    inplace_outputs: dict[int, int] | None = None, verbose: bool = False,
+                    **options: Any) -> CompiledProgram:
+    """Generate, build and load the kernel for `program` on the inputs' device (sm_100 required)."""
+    flat, _ = tree_flatten(example_inputs)
+    if not flat or any(not isinstance(x, torch.Tensor) for x in flat):
+        raise TypeError("trainkernel: nonempty tensor inputs required")
+    if len(flat) != len(program.inputs):
+        raise ValueError("trainkernel: input count differs from the program signature")
+    if not torch.cuda.is_available() or any(x.device.type != "cuda" for x in flat):
+        raise RuntimeError("trainkernel: CUDA sm_100a GPU required; CPU IR inspection is available through capture()")
+    device = flat[0].device
+    if any(x.device != device for x in flat):
+        raise ValueError("trainkernel: all inputs must use the same CUDA device")
+    capability = torch.cuda.get_device_capability(device)
+    if capability[0] != 10:
+        raise RuntimeError(f"trainkernel: an sm_100 (B200-class) GPU is required, found compute capability {capability[0]}.{capability[1]}")
+    generated = generate(program, inplace_outputs=inplace_outputs, **options)
+    if any(flat[i].requires_grad for i in (inplace_outputs or {}).values()):
+        raise ValueError("trainkernel: inplace targets must be detached from autograd")
+    cubin = build_cubin(generated.source, verbose=verbose)
+    with torch.cuda.device(device):
+        torch.cuda.current_stream(device)     # make sure the primary context exists before the shim retains it
+        module = _Module(generated, cubin, device)
+    runner = CompiledProgram(program, generated, module, device, inplace_outputs)
+    runner._validate_inputs(tuple(flat))
+    return runner
