@@ -503,7 +503,7 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
 // re-rounded to a 16-bit type first (a cast folded into the load).  32x32 output tile per
 // block-iteration, 128 compute threads each owning a 2x4 strip.
 // ----------------------------------------------------------------------------
-struct SimtSmem { float a[32][33]; float b[32][36]; };
+struct alignas(16) SimtSmem { float a[32][33]; float pad[4]; float b[32][36]; };
 
 template <typename TA, typename RA, typename TB, typename RB, typename Epi, typename Params>
 __device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm, const TA* A, int64_t a_rs, int64_t a_ks,

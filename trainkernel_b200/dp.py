@@ -1,0 +1,106 @@
+"""Batch-sharded data parallelism for a compiled training step (one process per GPU).
+
+The reference has no distributed code (reference: README.md:128).  This module
+adds the one exchange a batch-sharded step needs: every rank runs the
+*gradient half* of the program on its rows of the batch, the gradients (and
+the loss) are averaged across ranks, and every rank runs the identical
+*update half* on identical inputs, so replicas stay bit-identical.  Because
+each rank's loss is a mean over its own rows and shards are equal-sized, the
+average of the local gradients is the full-batch gradient.
+
+`reduce="nccl"` launches the two halves as separate kernels with one
+`torch.distributed.all_reduce(AVG)` over a flat gradient buffer between them
+(a CUDA-graph-capturable sequence on one stream).
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Sequence
+
+import torch
+import torch.distributed as dist
+from torch.utils._pytree import tree_flatten, tree_unflatten
+
+from . import runtime
+from .frontend import capture
+from .passes import split_at_gradients
+
+
+def shard_rows(batch: int, rank: int, world: int) -> slice:
+    """Rows of the global batch owned by `rank`; the batch must divide evenly."""
+    if batch % world:
+        raise ValueError("trainkernel: global batch must divide evenly across ranks")
+    per = batch // world
+    return slice(rank * per, (rank + 1) * per)
+
+
+class ShardedTrainingStep:
+    """`(state, *data) -> (loss, grads, state)` with gradients averaged over a process group.
+
+    `example_inputs` hold this rank's shard.  State tensors are updated in
+    place, as with `compile_training`.  The returned loss and gradients are the
+    cross-rank averages and live in buffers owned by this object (reused by the
+    next call).
+    """
+
+    def __init__(self, fn: Callable[..., Any], example_inputs: Sequence[Any], *, group: Any = None,
+                 reduce: str = "nccl", **options: Any) -> None:
+        if reduce != "nccl":
+            raise ValueError("trainkernel: reduce must be 'nccl'")
+        if "inplace_outputs" in options:
+            raise ValueError("trainkernel: the sharded step derives its own state mapping")
+        self.group = group
+        program, output_tree = capture(fn, example_inputs)
+        flat, self.input_tree = tree_flatten(tuple(example_inputs))
+        state_leaves, _ = tree_flatten(example_inputs[0])
+        n = self.count = len(state_leaves)
+        self.output_tree = output_tree
+        self.program = program
+        gradient_half, update_half = split_at_gradients(program, n)
+        self.gradient = runtime.compile_program(gradient_half, flat, **options)
+        device = self.device = self.gradient.device
+        # loss and every gradient live back to back in one FP32 buffer so a single collective covers them
+        sizes = [1] + [spec_numel(s.shape) for s in gradient_half.outputs[1:]]
+        for spec in gradient_half.outputs:
+            if spec.dtype != "float32":
+                raise ValueError("trainkernel: the sharded step exchanges FP32 losses and gradients")
+        padded = [-(-size // 64) * 64 for size in sizes]          # keep every slice 256-byte aligned
+        self.flat = torch.zeros(sum(padded), dtype=torch.float32, device=device)
+        self.views = []
+        cursor = 0
+        for spec, size, pad in zip(gradient_half.outputs, sizes, padded):
+            self.views.append(self.flat[cursor:cursor + size].view(spec.shape))
+            cursor += pad
+        update_inputs = tuple(state_leaves) + tuple(self.views[1:])
+        self.update = runtime.compile_program(update_half, update_inputs, inplace_outputs={i: i for i in range(n)}, **options)
+        self.gradient_workspace = torch.empty(self.gradient.generated.workspace_elements, dtype=torch.float32, device=device)
+        self.update_workspace = torch.empty(self.update.generated.workspace_elements, dtype=torch.float32, device=device)
+
+    @property
+    def kernels_per_step(self) -> int:
+        return 2
+
+    def __call__(self, *args: Any):
+        flat, tree = tree_flatten(args)
+        if tree != self.input_tree:
+            raise ValueError("trainkernel: runtime input pytree differs from the compiled signature")
+        flat = tuple(flat)
+        self.gradient._validate_inputs(flat)
+        state = flat[:self.count]
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self.gradient.module.launch(flat, self.views, self.gradient_workspace, stream)
+        if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            dist.all_reduce(self.flat, op=dist.ReduceOp.AVG, group=self.group)
+        self.update.module.launch(state + tuple(self.views[1:]), state, self.update_workspace, stream)
+        torch.autograd.graph.increment_version(list(state))
+        return tree_unflatten([self.views[0], *self.views[1:], *state], self.output_tree)
+
+    def status(self) -> None:
+        self.gradient.status()
+        self.update.status()
+
+
+def spec_numel(shape: tuple[int, ...]) -> int:
+    total = 1
+    for extent in shape:
+        total *= extent
+    return total
