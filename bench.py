@@ -134,7 +134,7 @@ def _leaves(state):
 def cpu_baseline(steps: int, warmup: int) -> dict:
     """Time the CPU oracle (IR interpreter, a port of the reference's reference.py) on the host cores.
 
-    A full medium-MLP step is ~9.4 TFLOP, so two bounded samples of the batch (128 and 256 rows,
+    A full medium-MLP step is ~9.4 TFLOP, so two bounded samples of the batch (512 and 1024 rows,
     full-size weights) are timed and the per-step time is extrapolated linearly in the row count.
     """
     import trainkernel_b200 as tk
@@ -149,7 +149,7 @@ def cpu_baseline(steps: int, warmup: int) -> dict:
         state.append((torch.rand((fan_in, fan_out), generator=gen) * 2 - 1) * bound)
         state.append(torch.zeros(fan_out))
     timings = {}
-    for rows in (128, 256):
+    for rows in (512, 1024):
         x = torch.randn((rows, MEDIUM_SIZES[0]), generator=gen).to(torch.bfloat16)
         t = torch.randn((rows, MEDIUM_SIZES[-1]), generator=gen).to(torch.bfloat16)
         fn = lambda s, xx, tt: workloads.mlp_master_step(s, xx, tt, 1e-3)  # noqa: E731
@@ -161,12 +161,12 @@ def cpu_baseline(steps: int, warmup: int) -> dict:
             if i >= warmup:
                 samples.append(time.perf_counter() - begin)
         timings[rows] = statistics.median(samples)
-    slope = (timings[256] - timings[128]) / 128.0
-    intercept = timings[128] - slope * 128.0
+    slope = (timings[1024] - timings[512]) / 512.0
+    intercept = timings[512] - slope * 512.0
     full = intercept + slope * MEDIUM_BATCH
     return {"value": 1.0 / full, "unit": "steps/s", "cores": threads, "kind": "port",
-            "sample": f"IR-interpreter oracle on 128 and 256 of {MEDIUM_BATCH} batch rows with full-size weights "
-                      f"({timings[128]:.3f} s, {timings[256]:.3f} s per step), extrapolated linearly in rows to {full:.1f} s per full step",
+            "sample": f"IR-interpreter oracle on 512 and 1024 of {MEDIUM_BATCH} batch rows with full-size weights "
+                      f"({timings[512]:.3f} s, {timings[1024]:.3f} s per step), extrapolated linearly in rows to {full:.1f} s per full step",
             "seconds_per_step_extrapolated": full}
 
 
