@@ -93,6 +93,22 @@ void tk_module_unload(tk_module* module);
 
 const char* tk_last_error(void);
 
+/* Size of the device-resident workspace that tk_module_launch_static_workspace lends to a kernel. */
+#define TK_STATIC_WORKSPACE_BYTES (4u << 20)
+
+/* Like tk_module_launch, but the workspace is a fixed TK_STATIC_WORKSPACE_BYTES array that lives in
+ * libtrainkernel_noalloc.so's device image, so neither the caller nor the library allocates.  It has
+ * no counterpart in the reference, whose callers always allocate a workspace tensor
+ * (trainkernel/runtime.py:58-64).  For callers that must not allocate when they launch a step:
+ * `workspace_bytes` is what the kernel's plan needs and is rejected with TK_E_CAPACITY when it exceeds
+ * the array; `device` is the ordinal the module was loaded on.  All calls on a device share the one
+ * array (overlapping launches race; nothing needs clearing between calls).  The first call on a device
+ * looks the array's address up through the CUDA runtime and should happen before any stream capture.
+ * On failure a message is written to `error` (may be NULL).  Exported by libtrainkernel_noalloc.so. */
+int tk_module_launch_static_workspace(tk_module* module, int device, const void* const* inputs,
+                                      void* const* outputs, size_t workspace_bytes, int grid,
+                                      void* stream, char* error, size_t error_capacity);
+
 /* Number of kernel launches issued through this library by the calling process. */
 uint64_t tk_launch_count(void);
 
