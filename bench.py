@@ -32,9 +32,9 @@ if str(ROOT) not in sys.path:
 
 MEDIUM_SIZES = (4096, 8192, 8192, 8192, 4096)
 MEDIUM_BATCH = 8192
-# DRAM bytes of one medium-MLP step kernel at N = 1 (ncu dram__bytes_read.sum + dram__bytes_write.sum);
-# None until a capture has been committed under profiles/.
-MEASURED_TRAFFIC_BYTES = None
+# DRAM bytes of one medium-MLP step kernel at N = 1 (ncu dram__bytes_read.sum + dram__bytes_write.sum,
+# one-pass capture of the full-size launch; see profiles/tk_step_c5_medium_mlp.md).
+MEASURED_TRAFFIC_BYTES = 14.52e9
 
 
 def _peaks() -> dict:
@@ -231,7 +231,13 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-small-configs", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--workload", default="c5", choices=["c5", "c5_half"],
+                        help="c5_half (2048-4096-4096-4096-2048, batch 4096) is the small case used for ncu captures")
+    parser.add_argument("--eager", action="store_true", help="launch the timed steps directly instead of replaying a CUDA graph")
     args = parser.parse_args()
+    global MEDIUM_SIZES, MEDIUM_BATCH
+    if args.workload == "c5_half":
+        MEDIUM_SIZES, MEDIUM_BATCH = (2048, 4096, 4096, 4096, 2048), 4096
     if args.impl == "reference":
         run_reference(args)
         return
@@ -254,7 +260,8 @@ def main() -> None:
     steps, warmup = args.steps, max(3, args.warmup)
 
     rows = dp.shard_rows(MEDIUM_BATCH, rank, world)
-    work = workloads.mlp_workload("c5_medium_mlp", MEDIUM_SIZES, MEDIUM_BATCH, seed=0, device=device, rows=rows)
+    work = workloads.mlp_workload("c5_medium_mlp" if args.workload == "c5" else "c5_half_mlp", MEDIUM_SIZES, MEDIUM_BATCH,
+                                  seed=0, device=device, rows=rows)
     state = work.state
     x0, t0 = work.batches[0]
     if world == 1:
@@ -276,12 +283,20 @@ def main() -> None:
     for i in range(warmup):
         step(state, *work.batches[i % len(work.batches)])
     barrier()
-    graph = torch.cuda.CUDAGraph()
     losses = []
-    with torch.cuda.graph(graph):
-        for i in range(steps):
-            out = step(state, *work.batches[i % len(work.batches)])
-            losses.append(out[0])
+    if args.eager:
+        class _Eager:
+            def replay(self):
+                losses.clear()
+                for i in range(steps):
+                    losses.append(step(state, *work.batches[i % len(work.batches)])[0])
+        graph = _Eager()
+    else:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(steps):
+                out = step(state, *work.batches[i % len(work.batches)])
+                losses.append(out[0])
     graph.replay()                       # one untimed replay: graph upload, allocator settled
     barrier()
     launches_before = runtime.library().tk_launch_count()
@@ -345,10 +360,11 @@ def main() -> None:
         "metric": "captured_step_throughput", "value": steps / (elapsed_ms * 1e-3), "unit": "steps/s",
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": elapsed_ms / steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "c5 medium MLP 4096-8192-8192-8192-4096, global batch 8192, BF16 compute / FP32 master, SGD lr 1e-3",
+        "config": {"workload": f"{args.workload} medium MLP {'-'.join(map(str, MEDIUM_SIZES))}, global batch {MEDIUM_BATCH}, BF16 compute / FP32 master, SGD lr 1e-3",
                    "global_batch": MEDIUM_BATCH, "rows_per_rank": work.batch, "resident_batches": len(work.batches),
                    "parallelism": f"dp{world} (batch-sharded, NCCL all-reduce of FP32 gradients)" if world > 1 else "single GPU, one kernel per step",
-                   "l2": "inputs larger than L2 (805 MB of FP32 weights, 134 MB per batch)", "graph_steps": steps},
+                   "l2": "inputs larger than L2 (FP32 weights %d MB, %d MB per batch)" % (work.weight_elements * 4 // 2**20, work.batch * (MEDIUM_SIZES[0] + MEDIUM_SIZES[-1]) * 2 // 2**20),
+                   "graph_steps": 0 if args.eager else steps},
         "latency_us": {"p50": round(statistics.median(samples), 1), "min": round(min(samples), 1), "max": round(max(samples), 1),
                        "replays": len(samples)},
         "clocks": clocks, "roofline": roofline, "e2e": e2e,
@@ -364,9 +380,14 @@ def main() -> None:
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(1, 1)
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Tearing an NCCL communicator down while CUDA graphs that captured its collectives are still
+        # alive can block forever; every rank has its result, so leave without the teardown.
+        barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def measure_e2e(step, state, work, steps: int, world: int, device) -> dict:
