@@ -66,6 +66,11 @@ int tk_module_launch(tk_module* module, const void* const* inputs, void* const* 
  * resident blocks per SM}.  Replaces `resource_usage()` (reference: trainkernel/codegen.py:889-895). */
 int tk_module_resource_usage(tk_module* module, int64_t out[4]);
 
+/* Launch the kernel with thread-block clusters of `size` CTAs (1 or 2; kernels generated with the
+ * two-CTA tcgen05 GEMM need 2).  Recomputes the co-resident capacity for clustered launches.  New on
+ * this back end: the reference's kernels have no cluster dimension (trainkernel/codegen.py:886). */
+int tk_module_set_cluster(tk_module* module, int size);
+
 /* Largest grid a cooperative launch of this kernel accepts on its device. */
 int tk_module_max_coresident_blocks(tk_module* module, int* out);
 

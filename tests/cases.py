@@ -19,12 +19,21 @@ def _rand(shape, dtype, device, seed):
     return torch.randn(shape, generator=gen, dtype=torch.float32).to(dtype).to(device)
 
 
-def gemm_case(m, n, k, a_major, b_major, dtype=BF16):
+def gemm_case(m, n, k, a_major, b_major, dtype=BF16, **options):
     """a @ b with either operand K-major or MN-major in memory."""
     def build(device):
         a = _rand((m, k), dtype, device, 1) if a_major == "k" else _rand((k, m), dtype, device, 1).t()
         b = _rand((n, k), dtype, device, 2).t() if b_major == "k" else _rand((k, n), dtype, device, 2)
-        return (lambda x, y: x @ y), (a, b), "compile", {}
+        return (lambda x, y: x @ y), (a, b), "compile", dict(options)
+    return build
+
+
+def mlp_case(sizes, batch, **options):
+    """BF16-compute / FP32-master MLP step of arbitrary layer sizes."""
+    def build(device):
+        work = workloads.mlp_workload("mlp", sizes, batch, seed=5, device=device, resident=1)
+        x, t = work.batches[0]
+        return work.fn(), (work.state, x, t), "compile_training", dict(options)
     return build
 
 
@@ -83,6 +92,14 @@ CASES = {
     "gemm_kk_big": gemm_case(384, 640, 1024, "k", "k"),
     "gemm_kn_f16": gemm_case(256, 192, 128, "k", "mn", F16),
     "gemm_kn_wide": gemm_case(2048, 4096, 256, "k", "mn"),
+    # two-CTA (cta_group::2) pair tiles, forced on small shapes and chosen automatically on the wide one above
+    "gemm2_kk": gemm_case(512, 512, 256, "k", "k", two_cta=True),
+    "gemm2_kn": gemm_case(512, 512, 256, "k", "mn", two_cta=True),
+    "gemm2_mk": gemm_case(512, 512, 256, "mn", "k", two_cta=True),
+    "gemm2_mn": gemm_case(512, 512, 256, "mn", "mn", two_cta=True),
+    "gemm2_ragged": gemm_case(300, 520, 200, "k", "mn", two_cta=True),
+    "gemm2_ragged_t": gemm_case(520, 264, 1000, "mn", "k", two_cta=True),
+    "gemm2_deep": gemm_case(1024, 768, 4096, "k", "mn", two_cta=True),
     # SIMT and GEMV paths
     "gemm_f32": gemm_case(65, 67, 17, "k", "mn", F32),
     "gemm_f32_t": gemm_case(33, 79, 47, "mn", "k", F32),
@@ -103,6 +120,8 @@ CASES = {
     "mlp_f16": native_mlp_case(17, 33, 65, 19, F16),
     "mlp_f32_one_block": native_mlp_case(7, 11, 17, 5, F32, max_blocks=1),
     "linear_module": _linear_module_case,
+    "mlp_2cta": mlp_case((512, 1024, 768, 512), 512, two_cta=True),
+    "mlp_1cta": mlp_case((512, 1024, 768, 512), 512, two_cta=False),
     # general subset
     "add_one_inplace": function_case(lambda x: x + 1, [(1000,)], inplace_outputs={0: 0}),
     "partial_reduce": function_case(lambda x: (x.sum((0, 2)), x.mean(1, keepdim=True), x.t().sum(0) if x.dim() == 2 else x.sum()), [(5, 7, 9)]),

@@ -144,5 +144,7 @@ def test_medium_mlp_plan_fits_and_uses_wide_tiles():
     g = generate(program, inplace_outputs={9 + i: i for i in range(8)})
     assert g.tensor_core_operations == 11 and g.direct_state_commits == 8
     assert g.grid == 148 and g.workspace_bytes < 2 * 2 ** 30
-    assert "tk::gemm_tc<256" in g.source
+    assert g.cluster == 2 and "tk::gemm_tc2<" in g.source and "tk::gemm_tc<" not in g.source   # pair tiles everywhere
+    single = generate(program, inplace_outputs={9 + i: i for i in range(8)}, two_cta=False)
+    assert single.cluster == 1 and "tk::gemm_tc<256" in single.source
     assert len(g.tensor_maps) == 22 and g.param_bytes <= 4096

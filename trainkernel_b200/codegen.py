@@ -76,6 +76,7 @@ class GeneratedKernel:
     staged_state_commits: int = 0
     param_bytes: int = 0
     workspace_bytes: int = 0
+    cluster: int = 1                      # thread-block cluster size the kernel must be launched with
 
 
 class _Body:
@@ -103,6 +104,7 @@ class _Emitter:
         self.maps: list[TensorMapSpec] = []
         self.functors: list[str] = []
         self.needs_simt = False
+        self.raster_group = 8
 
     # -- addressing ------------------------------------------------------------------
     def pointer(self, buffer: str, dtype: str, const: bool) -> str:
@@ -262,7 +264,14 @@ class _Emitter:
         epi = self.functor(unit)
         m, n, k = unit.mnk
         a, b = unit.a, unit.b
-        if unit.path == "tc":
+        if unit.path == "tc2":
+            ia, a_mn = self._tensor_map(a, m, k, 128)
+            flipped = type(b)(b.buffer, b.dtype, b.round_to, b.offset, (b.strides[1], b.strides[0]))
+            ib, b_mn = self._tensor_map(flipped, n, k, 128)
+            fmt = 1 if a.dtype == "bfloat16" else 0
+            body.emit(f"tk::gemm_tc2<{str(a_mn).lower()}, {str(b_mn).lower()}, {fmt}, {self.raster_group}, {epi}>"
+                      f"(c, P, &P.maps[{ia}], &P.maps[{ib}], {m}, {n}, {k}, {base}LL);")
+        elif unit.path == "tc":
             ia, a_mn = self._tensor_map(a, m, k, 128)
             # B is [K, N]: its "rows" are N and strides are (stride along N, stride along K)
             flipped = type(b)(b.buffer, b.dtype, b.round_to, b.offset, (b.strides[1], b.strides[0]))
@@ -467,7 +476,7 @@ class _Emitter:
             base = 0
             members = [u for u in plan.units if u.stage == stage]
             # GEMM units first: the specialised warps drain them before joining the block-wide loops
-            for unit in sorted(members, key=lambda u: (u.kind != "gemm", u.path != "tc", u.index)):
+            for unit in sorted(members, key=lambda u: (u.kind != "gemm", u.path not in ("tc", "tc2"), u.index)):
                 body.emit("{")
                 body.depth += 1
                 if unit.kind == "gemm":
@@ -485,7 +494,7 @@ class _Emitter:
         n_maps = max(1, len(self.maps))
         use_tc = "true" if plan.uses_tc else "false"
         header = [
-            '#include "tk_device.cuh"',
+            '#include "tk_gemm_2cta.cuh"' if plan.two_cta else '#include "tk_device.cuh"',
             "struct Params {",
             f"    CUtensorMap maps[{n_maps}];",
             f"    const void* in[{n_in}];",
@@ -509,6 +518,7 @@ class _Emitter:
             entry.append("    __shared__ tk::SimtSmem simt;")
         entry += [
             "    tk::Ctx c;",
+            "    tk::ctx_init2(c, P.sync, P.status, P.timeout_ns, P.arrivals, &shared_state, dyn_smem);" if plan.two_cta else
             f"    tk::ctx_init(c, P.sync, P.status, P.timeout_ns, P.arrivals, &shared_state, dyn_smem, {use_tc});",
         ]
         if stage_stamps:
@@ -516,7 +526,7 @@ class _Emitter:
         tail = []
         if stage_stamps:
             tail.append(f"    __syncthreads();\n    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[{plan.stages}] = tk::global_timer_ns();")
-        tail += [f"    tk::ctx_finish(c, {use_tc});", "}", ""]
+        tail += ["    tk::ctx_finish2(c);" if plan.two_cta else f"    tk::ctx_finish(c, {use_tc});", "}", ""]
         return "\n".join(header + self.functors + entry + [body.text()] + tail)
 
 
@@ -544,7 +554,7 @@ def _check_broadcasts(program: Program) -> None:
 
 def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = None, fuse_pointwise: bool = True,
                  fuse_epilogues: bool = True, max_blocks: int | None = None, tensor_cores: bool = True,
-                 block_n: int | None = None) -> Plan:
+                 block_n: int | None = None, two_cta: bool | None = None) -> Plan:
     """Validate, canonicalise and plan `program` (no code is emitted)."""
     validate(program)
     from .passes import canonicalize_transposed_mm
@@ -570,7 +580,7 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
         if output.buffer not in produced:
             raise ValueError("trainkernel: inplace outputs must be computed values, not input views")
     return Planner(program, inplace_outputs=mapping, fuse_pointwise=fuse_pointwise, fuse_epilogues=fuse_epilogues,
-                   max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n).plan()
+                   max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n, two_cta=two_cta).plan()
 
 
 _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shared_skew", "split_k_gemv",
@@ -580,7 +590,7 @@ _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shar
 def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: bool = True,
              max_blocks: int | None = None, inplace_outputs: dict[int, int] | None = None,
              tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
-             **reference_knobs) -> GeneratedKernel:
+             two_cta: bool | None = None, raster_group: int | None = None, **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -597,8 +607,13 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     if type(blocks_per_sm) is not int or not 1 <= blocks_per_sm <= 8:
         raise ValueError("trainkernel: blocks_per_sm must be between 1 and 8")
     plan = plan_program(program, inplace_outputs=inplace_outputs, fuse_pointwise=fuse_pointwise,
-                        fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n)
+                        fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n,
+                        two_cta=two_cta)
     emitter = _Emitter(plan)
+    if raster_group is not None:
+        if type(raster_group) is not int or not 1 <= raster_group <= 64:
+            raise ValueError("trainkernel: raster_group must be between 1 and 64")
+        emitter.raster_group = raster_group
     source = emitter.kernel(stage_stamps)
     n_in, n_out = max(1, len(plan.program.inputs)), max(1, len(plan.program.outputs))
     n_maps = max(1, len(emitter.maps))
@@ -632,4 +647,5 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         staged_state_commits=len(plan.staged_commits),
         param_bytes=param_bytes,
         workspace_bytes=plan.workspace_bytes,
+        cluster=2 if plan.two_cta else 1,
     )

@@ -23,7 +23,9 @@ constexpr int kEpiThreads = 128;
 constexpr int BM = 128;                // UMMA M
 constexpr int BK = 64;                 // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kStages = 4;
+constexpr int kStages = 4;            // cta_group::1 ring: 4 x 48 KiB
+constexpr int kStages2 = 6;           // cta_group::2 ring: 6 x 32 KiB
+constexpr int kMaxStages = 8;
 constexpr int kMaxBN = 256;
 constexpr int kSlotA = BM * BK * 2;    // 16 KiB
 constexpr int kSlotB = kMaxBN * BK * 2;  // 32 KiB
@@ -116,8 +118,8 @@ __host__ __device__ constexpr uint32_t umma_idesc(int fmt, int a_major, int b_ma
 // per-CTA context
 // ----------------------------------------------------------------------------
 struct SharedState {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
@@ -166,6 +168,7 @@ struct Ctx {
         return true;
     }
     __device__ __forceinline__ void advance_slot() { if (++slot == kStages) { slot = 0; slot_phase ^= 1; } }
+    __device__ __forceinline__ void advance_slot2() { if (++slot == kStages2) { slot = 0; slot_phase ^= 1; } }
     __device__ __forceinline__ void advance_acc() { if (++acc == 2) { acc = 0; acc_phase ^= 1; } }
 };
 

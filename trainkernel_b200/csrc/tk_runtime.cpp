@@ -35,7 +35,7 @@ int fail(int code, const char* format, ...) {
     X(cuModuleLoadData) X(cuModuleUnload) X(cuModuleGetFunction) X(cuFuncSetAttribute)              \
     X(cuFuncGetAttribute) X(cuOccupancyMaxActiveBlocksPerMultiprocessor) X(cuLaunchKernelEx)        \
     X(cuMemAlloc) X(cuMemFree) X(cuMemsetD8) X(cuMemcpyDtoH) X(cuStreamSynchronize)                 \
-    X(cuTensorMapEncodeTiled) X(cuGetErrorString)
+    X(cuTensorMapEncodeTiled) X(cuGetErrorString) X(cuOccupancyMaxActiveClusters)
 
 struct Driver {
 #define X(sym) decltype(&sym) sym##_ = nullptr;
@@ -112,6 +112,8 @@ struct tk_module {
     std::atomic<uint32_t> arrivals{0};
     int sm_count = 0;
     int blocks_per_sm = 0;
+    int cluster = 1;
+    int max_blocks = 0;               // co-resident capacity for the current cluster size
     size_t param_bytes = 0;
 
     CUdeviceptr sync_slot(uint32_t i) const { return state + static_cast<size_t>(i) * kSyncStride; }
@@ -159,6 +161,7 @@ int tk_module_load(const void* cubin, size_t cubin_bytes, const char* entry, int
                         "cuOccupancyMaxActiveBlocksPerMultiprocessor")))
             break;
         if (m->blocks_per_sm < 1) { rc = fail(TK_E_CAPACITY, "trainkernel: kernel has no resident blocks"); break; }
+        m->max_blocks = m->sm_count * m->blocks_per_sm;
         if ((rc = check(g_driver.cuMemAlloc_(&m->state, m->state_bytes()), "cuMemAlloc(kernel state)"))) break;
         if ((rc = check(g_driver.cuMemsetD8_(m->state, 0, m->state_bytes()), "cuMemsetD8(kernel state)"))) break;
     } while (false);
@@ -189,9 +192,9 @@ void tk_module_unload(tk_module* m) {
 int tk_module_launch(tk_module* m, const void* const* inputs, void* const* outputs, void* workspace, int grid, void* stream) {
     if (!m || grid < 1 || (m->n_inputs > 0 && !inputs) || (m->n_outputs > 0 && !outputs))
         return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_launch");
-    if (grid > m->sm_count * m->blocks_per_sm)
-        return fail(TK_E_CAPACITY, "trainkernel: grid %d exceeds the %d co-resident blocks a cooperative launch allows", grid,
-                    m->sm_count * m->blocks_per_sm);
+    if (grid > m->max_blocks || grid % m->cluster)
+        return fail(TK_E_CAPACITY, "trainkernel: grid %d exceeds the %d co-resident blocks a cooperative launch allows (cluster size %d)", grid,
+                    m->max_blocks, m->cluster);
     // Kernel parameter block: tensor maps, input pointers, output pointers, then the scalars.
     alignas(64) unsigned char block[4096];
     if (m->param_bytes > sizeof(block)) return fail(TK_E_ARGUMENT, "trainkernel: parameter block too large");
@@ -233,10 +236,13 @@ int tk_module_launch(tk_module* m, const void* const* inputs, void* const* outpu
     memcpy(cursor + 40, &arrivals, 4);
 
     ContextScope scope(m->context);
-    CUlaunchAttribute attribute;
-    memset(&attribute, 0, sizeof(attribute));
-    attribute.id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE;
-    attribute.value.cooperative = 1;
+    CUlaunchAttribute attribute[2];
+    memset(attribute, 0, sizeof(attribute));
+    attribute[0].id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE;
+    attribute[0].value.cooperative = 1;
+    attribute[1].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attribute[1].value.clusterDim.x = static_cast<unsigned>(m->cluster);
+    attribute[1].value.clusterDim.y = attribute[1].value.clusterDim.z = 1;
     CUlaunchConfig config;
     memset(&config, 0, sizeof(config));
     config.gridDimX = static_cast<unsigned>(grid);
@@ -245,8 +251,8 @@ int tk_module_launch(tk_module* m, const void* const* inputs, void* const* outpu
     config.blockDimY = config.blockDimZ = 1;
     config.sharedMemBytes = static_cast<unsigned>(m->dynamic_smem);
     config.hStream = static_cast<CUstream>(stream);
-    config.attrs = &attribute;
-    config.numAttrs = 1;
+    config.attrs = attribute;
+    config.numAttrs = m->cluster > 1 ? 2 : 1;
     void* params[1] = {block};
     if (int rc = check(g_driver.cuLaunchKernelEx_(&config, m->function, params, nullptr), "cuLaunchKernelEx")) return rc;
     g_launches.fetch_add(1);
@@ -269,7 +275,37 @@ int tk_module_resource_usage(tk_module* m, int64_t out[4]) {
 
 int tk_module_max_coresident_blocks(tk_module* m, int* out) {
     if (!m || !out) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_max_coresident_blocks");
-    *out = m->sm_count * m->blocks_per_sm;
+    *out = m->max_blocks;
+    return 0;
+}
+
+int tk_module_set_cluster(tk_module* m, int size) {
+    if (!m || (size != 1 && size != 2)) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_set_cluster");
+    if (size == 1) {
+        m->cluster = 1;
+        m->max_blocks = m->sm_count * m->blocks_per_sm;
+        return 0;
+    }
+    ContextScope scope(m->context);
+    CUlaunchAttribute attribute;
+    memset(&attribute, 0, sizeof(attribute));
+    attribute.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attribute.value.clusterDim.x = static_cast<unsigned>(size);
+    attribute.value.clusterDim.y = attribute.value.clusterDim.z = 1;
+    CUlaunchConfig config;
+    memset(&config, 0, sizeof(config));
+    config.gridDimX = static_cast<unsigned>(m->sm_count - m->sm_count % size);
+    config.gridDimY = config.gridDimZ = 1;
+    config.blockDimX = static_cast<unsigned>(m->threads);
+    config.blockDimY = config.blockDimZ = 1;
+    config.sharedMemBytes = static_cast<unsigned>(m->dynamic_smem);
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (int rc = check(g_driver.cuOccupancyMaxActiveClusters_(&clusters, m->function, &config), "cuOccupancyMaxActiveClusters")) return rc;
+    if (clusters < 1) return fail(TK_E_CAPACITY, "trainkernel: no cluster of %d blocks can be resident", size);
+    m->cluster = size;
+    m->max_blocks = clusters * size;
     return 0;
 }
 

@@ -148,12 +148,13 @@ class Plan:
     grid: int
     tensor_core_units: int
     uses_tc: bool
+    two_cta: bool = False
 
 
 class Planner:
     def __init__(self, program: Program, *, inplace_outputs: dict[int, int] | None = None,
                  fuse_pointwise: bool = True, fuse_epilogues: bool = True, max_blocks: int | None = None,
-                 tensor_cores: bool = True, block_n: int | None = None):
+                 tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None):
         self.program = program
         self.inplace = dict(inplace_outputs or {})
         self.fuse_pointwise = fuse_pointwise
@@ -161,6 +162,7 @@ class Planner:
         self.max_blocks = max_blocks
         self.tensor_cores = tensor_cores
         self.forced_block_n = block_n
+        self.two_cta = two_cta
         self.ops = list(program.operations)
         self.index = {op.output.buffer: i for i, op in enumerate(self.ops)}
         self.producer = {op.output.buffer: op for op in self.ops}
@@ -627,16 +629,27 @@ class Planner:
         tc_units = 0
         for unit in units:
             self._size_unit(unit)
-            if unit.kind == "gemm" and unit.path == "tc":
+            if unit.kind == "gemm" and unit.path in ("tc", "tc2"):
                 tc_units += 1
+        # Two-CTA pair tiles (256 x 256) when every tensor-core GEMM is large enough to keep the
+        # clusters busy; a kernel uses one cta_group for all of its tcgen05 instructions.
+        tc = [u for u in units if u.kind == "gemm" and u.path == "tc"]
+        pair_tiles = [-(-u.mnk[0] // 256) * -(-u.mnk[1] // 256) for u in tc]
+        eligible = bool(tc) and all(u.mnk[0] >= 256 and u.mnk[1] >= 256 for u in tc)
+        two_cta = eligible and min(pair_tiles) >= 64 if self.two_cta is None else bool(self.two_cta and eligible)
+        if two_cta:
+            for unit, tiles in zip(tc, pair_tiles):
+                unit.path, unit.block_n, unit.items = "tc2", 256, 2 * tiles
         per_stage = [0] * stage_count
         for unit in units:
             per_stage[unit.stage] += unit.items
         grid = max(1, min(SM_COUNT, max(per_stage)))
         if self.max_blocks is not None:
             grid = max(1, min(grid, self.max_blocks))
+        if two_cta:
+            grid = max(2, grid - grid % 2)
         return Plan(program, sorted(units, key=lambda u: (u.stage, u.index)), stage_count, storage, dtypes, shapes,
-                    max(total, ALIGN), inlined, direct, staged, native, grid, tc_units, tc_units > 0)
+                    max(total, ALIGN), inlined, direct, staged, native, grid, tc_units, tc_units > 0, two_cta)
 
     # -- helpers ---------------------------------------------------------------------
     def _refs(self, expr) -> set[str]:

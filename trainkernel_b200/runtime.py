@@ -97,6 +97,7 @@ def library() -> ctypes.CDLL:
         lib.tk_module_set_timeout.argtypes = [p, u64]
         lib.tk_module_set_expected_arrivals.argtypes = [p, u32]
         lib.tk_module_stage_stamps.argtypes = [p, p, ctypes.POINTER(u64), i32]
+        lib.tk_module_set_cluster.argtypes = [p, i32]
         lib.tk_module_unload.argtypes = [p]
         lib.tk_module_unload.restype = None
         _library = lib
@@ -110,7 +111,7 @@ def _raise(code: int) -> None:
 
 def build_cubin(source: str, *, verbose: bool = False) -> bytes:
     """nvcc-compile generated source to an sm_100a cubin; cached by content hash."""
-    header = (CSRC_DIR / "tk_device.cuh").read_bytes()
+    header = (CSRC_DIR / "tk_device.cuh").read_bytes() + (CSRC_DIR / "tk_gemm_2cta.cuh").read_bytes()
     digest = hashlib.sha256(source.encode() + b"\0" + header + b"\0" + " ".join(NVCC_FLAGS).encode()).hexdigest()[:32]
     cached = CACHE_DIR / f"{digest}.cubin"
     if cached.exists():
@@ -171,10 +172,16 @@ class _Module:
             _raise(code)
         self.handle = handle
         self.lib = lib
+        if generated.cluster > 1:
+            code = lib.tk_module_set_cluster(handle, generated.cluster)
+            if code:
+                _raise(code)
         limit = ctypes.c_int()
         if lib.tk_module_max_coresident_blocks(handle, ctypes.byref(limit)):
             _raise(1)
         self.grid = max(1, min(generated.grid, limit.value))
+        if generated.cluster > 1:
+            self.grid -= self.grid % generated.cluster
         self.n_in = max(1, generated.input_count)
         self.n_out = max(1, generated.output_count)
 
