@@ -18,7 +18,7 @@ from dataclasses import dataclass, field
 from math import prod
 
 from .ir import Operation, Program, TensorSpec, row_major, validate
-from .plan import (ELEMENT_BYTES, THREADS, Access, Apply, Const, Load, Plan, Planner, Ref, Unit)
+from .plan import (ELEMENT_BYTES, THREADS, Access, Apply, Const, Load, Plan, Planner, Ref, Unit, point_unroll)
 
 CTYPE = {"float32": "float", "float16": "__half", "bfloat16": "__nv_bfloat16"}
 ROUND = {"float32": "tk::F32", "float16": "tk::F16", "bfloat16": "tk::BF16"}
@@ -101,10 +101,17 @@ class _Body:
 class _Emitter:
     def __init__(self, plan: Plan):
         self.plan = plan
+        read_anywhere = set()
+        for unit in plan.units:
+            read_anywhere |= unit.reads
+        # buffers nobody reads back inside the kernel: written (or, for in-place state, read) exactly once late in the step
+        self.write_once = {b for b, where in plan.storage.items() if where[0] == "out" and b not in read_anywhere}
+        self.state_inputs = {plan.program.inputs[i].buffer for i in set(plan.direct_commits.values()) | set(plan.staged_commits.values())}
         self.maps: list[TensorMapSpec] = []
         self.functors: list[str] = []
         self.needs_simt = False
         self.raster_group = 8
+        self.rows = False
 
     # -- addressing ------------------------------------------------------------------
     def pointer(self, buffer: str, dtype: str, const: bool) -> str:
@@ -128,8 +135,29 @@ class _Emitter:
         return " + ".join(terms) if terms else "0LL"
 
     # -- expressions -----------------------------------------------------------------
-    def value(self, expr, body: _Body, env: dict, width: str, coords: list[str], nvalid: str) -> str:
-        """Emit code computing `expr` for `width` consecutive elements along the last dim; returns the array name."""
+    # Values are emitted either as `float v[W]` (one run of W consecutive elements) or, inside GEMM
+    # epilogue functors, as `float v[R][W]` (R such runs in different rows, all loads issued before
+    # any store).  `self.rows` selects the second form; coordinates may then mention the row index `r`.
+    def _decl(self, name: str, width: str) -> str:
+        return f"float {name}[R][{width}];" if self.rows else f"float {name}[{width}];"
+
+    def _loop(self, width: str) -> str:
+        inner = f"_Pragma(\"unroll\") for (int j = 0; j < {width}; ++j)"
+        return f"_Pragma(\"unroll\") for (int r = 0; r < R; ++r) {inner}" if self.rows else inner
+
+    def _row_loop(self) -> str:
+        return "_Pragma(\"unroll\") for (int r = 0; r < R; ++r) " if self.rows else ""
+
+    @property
+    def _at(self) -> str:
+        return "[r][j]" if self.rows else "[j]"
+
+    @property
+    def _row(self) -> str:
+        return "[r]" if self.rows else ""
+
+    def value(self, expr, body: _Body, env: dict, width: str, coords: list[str], nvalid: str, vdim: int = -1) -> str:
+        """Emit code computing `expr` for `width` consecutive elements along dim `vdim` (default: last); returns the array name."""
         key = id(expr)
         if key in env:
             return env[key]
@@ -137,8 +165,8 @@ class _Emitter:
             return env["ref:" + expr.buffer]
         if isinstance(expr, Const):
             name = body.temp("k")
-            body.emit(f"float {name}[{width}];")
-            body.emit(f"_Pragma(\"unroll\") for (int j = 0; j < {width}; ++j) {name}[j] = {_literal(expr.value)};")
+            body.emit(self._decl(name, width))
+            body.emit(f"{self._loop(width)} {name}{self._at} = {_literal(expr.value)};")
             env[key] = name
             return name
         if isinstance(expr, Load):
@@ -148,9 +176,10 @@ class _Emitter:
                 return env[cache_key]
             name = body.temp("l")
             address = self._affine(access.offset, access.strides, coords, False)
-            step = access.strides[-1] if access.strides else 0
-            body.emit(f"float {name}[{width}];")
-            body.emit(f"tk::ld_row_strided<{width}>({self.pointer(access.buffer, access.dtype, True)} + ({address}), {step}LL, {nvalid}, {name});")
+            step = access.strides[vdim] if access.strides else 0
+            body.emit(self._decl(name, width))
+            loader = "ld_row_stream" if access.buffer in self.state_inputs and access.dtype == "float32" else "ld_row_strided"
+            body.emit(f"{self._row_loop()}tk::{loader}<{width}>({self.pointer(access.buffer, access.dtype, True)} + ({address}), {step}LL, {nvalid}, {name}{self._row});")
             env[cache_key] = name
             env[key] = name
             return name
@@ -161,11 +190,11 @@ class _Emitter:
             if isinstance(arg, Const):
                 args.append(_literal(arg.value))
             else:
-                args.append(self.value(arg, body, env, width, coords, nvalid) + "[j]")
+                args.append(self.value(arg, body, env, width, coords, nvalid, vdim) + self._at)
         formula = self.formula(op, args)
         name = body.temp("v")
-        body.emit(f"float {name}[{width}];")
-        body.emit(f"_Pragma(\"unroll\") for (int j = 0; j < {width}; ++j) {name}[j] = {ROUND[op.output.dtype]}::rnd({formula});")
+        body.emit(self._decl(name, width))
+        body.emit(f"{self._loop(width)} {name}{self._at} = {ROUND[op.output.dtype]}::rnd({formula});")
         env[key] = name
         return name
 
@@ -200,6 +229,14 @@ class _Emitter:
             return a[0]
         raise ValueError(f"trainkernel: unsupported pointwise operation {kind}")
 
+    def _preload(self, expr, body: _Body, env: dict, width: str, coords: list[str], nvalid: str) -> None:
+        """Emit only the loads of `expr` (cached in `env`), so they can all be in flight before any store."""
+        if isinstance(expr, Load):
+            self.value(expr, body, env, width, coords, nvalid)
+        elif isinstance(expr, Apply):
+            for arg in expr.args:
+                self._preload(arg, body, env, width, coords, nvalid)
+
     def dag(self, unit: Unit, body: _Body, env: dict, width: str, coords: list[str], nvalid: str) -> None:
         """Members in order, then the unit's stores, for `width` elements at `coords`."""
         for member in unit.members:
@@ -210,41 +247,78 @@ class _Emitter:
             if unit.phase == "partial":
                 continue
             address = self._affine(0, dense, coords, False)
-            body.emit(f"tk::st_row<{width}>({self.pointer(store.buffer, store.dtype, False)} + ({address}), {nvalid}, {env['ref:' + store.buffer]});")
+            storer = "st_row_stream" if store.buffer in self.write_once else "st_row"
+            body.emit(f"{self._row_loop()}tk::{storer}<{width}>({self.pointer(store.buffer, store.dtype, False)} + ({address}), {nvalid}, {env['ref:' + store.buffer]}{self._row});")
 
     # -- units -------------------------------------------------------------------------
     def functor(self, unit: Unit) -> str:
-        """Epilogue functor of a GEMM unit: rounds the accumulator, runs the DAG, stores."""
+        """Epilogue functor of a GEMM unit: rounds the accumulator, runs the DAG, stores.
+
+        `run_rows<R, W>` handles R runs of W consecutive columns, run r in row `x0 + r * rs`;
+        rows at or beyond M get a zero element count, which turns their loads and stores off.
+        `run<W>` is the single-run form.
+        """
         op = unit.root
         name = f"Epi_{unit.name}"
         body = _Body()
         body.depth = 2
         env: dict = {}
-        coords = ["x0", "x1"]
+        self.rows = True
+        coords = ["(x0 + r * rs)", "x1"]
+        body.emit("int nv[R];")
+        body.emit(f"_Pragma(\"unroll\") for (int r = 0; r < R; ++r) nv[r] = (x0 + r * rs < {unit.mnk[0]}) ? nvalid : 0;")
         root = body.temp("v")
         rounding = ROUND[op.output.dtype]
         if op.op == "addmm":
             alpha, beta = op.attrs.get("alpha", 1), op.attrs.get("beta", 1)
             if unit.bias is not None:
-                bias = self.value(unit.bias, body, env, "W", coords, "nvalid")
+                bias = self.value(unit.bias, body, env, "W", coords, "nv[r]")
             if alpha == 0 and beta == 0:
                 combine = "0.0f"
             elif beta == 0:
-                combine = f"({_literal(alpha)} * (acc[j]))"
+                combine = f"({_literal(alpha)} * (acc[r][j]))"
             elif alpha == 0:
-                combine = f"({_literal(beta)} * ({bias}[j]))"
+                combine = f"({_literal(beta)} * ({bias}[r][j]))"
             else:
-                combine = f"({_literal(alpha)} * (acc[j]) + {_literal(beta)} * ({bias}[j]))"
+                combine = f"({_literal(alpha)} * (acc[r][j]) + {_literal(beta)} * ({bias}[r][j]))"
         else:
-            combine = "acc[j]"
-        body.emit(f"float {root}[W];")
-        body.emit(f"_Pragma(\"unroll\") for (int j = 0; j < W; ++j) {root}[j] = {rounding}::rnd({combine});")
+            combine = "acc[r][j]"
+        body.emit(f"float {root}[R][W];")
+        body.emit(f"{self._loop('W')} {root}[r][j] = {rounding}::rnd({combine});")
         env["ref:" + op.output.buffer] = root
-        self.dag(unit, body, env, "W", coords, "nvalid")
+        self.dag(unit, body, env, "W", coords, "nv[r]")
+        self.rows = False
+        wide = any(ELEMENT_BYTES[s.dtype] == 4 for s in unit.stores)
+        # tile-shaped operands the epilogue reads (same row/column as the accumulator): worth prefetching into L2
+        fetched: list[Access] = []
+
+        def collect(expr) -> None:
+            if isinstance(expr, Load):
+                a = expr.access
+                if a.strides[0] != 0 and a.strides[1] == 1 and a not in fetched:
+                    fetched.append(a)
+            elif isinstance(expr, Apply):
+                for arg in expr.args:
+                    collect(arg)
+
+        for expr in unit.exprs.values():
+            collect(expr)
+        if unit.bias is not None:
+            collect(unit.bias)
+        prefetch = "".join(
+            f"        tk::prefetch_l2({self.pointer(a.buffer, a.dtype, True)} + ({a.offset}LL + (int64_t)row * {a.strides[0]}LL + col0), ncols * {ELEMENT_BYTES[a.dtype]});\n"
+            for a in fetched)
         self.functors.append(
             f"struct {name} {{\n"
-            f"    template <int W> static __device__ __forceinline__ void run(const Params& P, int x0, int x1, int nvalid, const float* acc) {{\n"
+            f"    static constexpr bool kWide = {'true' if wide else 'false'};   // stores FP32 tiles: prefer 4-column runs\n"
+            f"    template <int R, int W> static __device__ __forceinline__ void run_rows(const Params& P, int x0, int rs, int x1, int nvalid, const float (*acc)[W]) {{\n"
             f"{body.text()}\n"
+            f"    }}\n"
+            f"    template <int W> static __device__ __forceinline__ void run(const Params& P, int x0, int x1, int nvalid, const float* acc) {{\n"
+            f"        run_rows<1, W>(P, x0, 0, x1, nvalid, reinterpret_cast<const float (*)[W]>(acc));\n"
+            f"    }}\n"
+            f"    static __device__ __forceinline__ void prefetch(const Params& P, int row, int col0, int ncols) {{\n"
+            f"{prefetch}"
             f"    }}\n}};\n")
         return name
 
@@ -346,15 +420,25 @@ class _Emitter:
                 return expr
 
             flat.exprs = {k: rebase(v) for k, v in unit.exprs.items()}
+            unroll = point_unroll(total)
             body.emit(f"for (int64_t it = tk::first_item({base}LL); it < {unit.items}LL; it += gridDim.x) {{")
             body.depth += 1
-            body.emit(f"const int64_t i0 = (it * {THREADS}LL + threadIdx.x) * 8;")
-            body.emit(f"if (i0 < {total}LL) {{")
-            body.depth += 1
-            body.emit(f"const int nvalid = (int)tk::imin(8, {total}LL - i0);")
-            self.dag(flat, body, {}, "8", ["i0"], "nvalid")
-            body.depth -= 1
-            body.emit("}")
+            # Each thread owns `unroll` chunks of 8 consecutive elements, {THREADS * 8} elements apart, so every
+            # 128-bit access of a warp is contiguous; all loads are issued before the first store.
+            envs = []
+            for u in range(unroll):
+                body.emit(f"const int64_t i{u} = (it * {unroll}LL + {u}LL) * {THREADS * 8}LL + threadIdx.x * 8;")
+                body.emit(f"const int n{u} = (int)tk::imin(8, tk::imax(0, {total}LL - i{u}));")
+                env: dict = {}
+                for expr in flat.exprs.values():
+                    self._preload(expr, body, env, "8", [f"i{u}"], f"n{u}")
+                envs.append(env)
+            for u in range(unroll):
+                body.emit(f"if (n{u} > 0) {{")
+                body.depth += 1
+                self.dag(flat, body, envs[u], "8", [f"i{u}"], f"n{u}")
+                body.depth -= 1
+                body.emit("}")
             body.depth -= 1
             body.emit("}")
             return
@@ -379,7 +463,7 @@ class _Emitter:
 
     def reduce(self, unit: Unit, body: _Body, base: int) -> None:
         outputs, size, parts = prod(unit.kept), prod(unit.reduced), unit.parts
-        chunk = -(-size // parts)
+        chunk = -(-(-(-size // parts)) // 4) * 4       # whole runs of 4 per part
         kept_rank = len(unit.kept)
         body.emit(f"// {unit.name}: {unit.root.op} {list(unit.kept)} <- {list(unit.reduced)} ({unit.strategy or 'finish'}, parts={parts})")
         scratch = None
@@ -403,6 +487,18 @@ class _Emitter:
             body.emit("}")
             return
 
+        loads: list[Access] = []
+
+        def gather(expr) -> None:
+            if isinstance(expr, Load):
+                loads.append(expr.access)
+            elif isinstance(expr, Apply):
+                for arg in expr.args:
+                    gather(arg)
+
+        gather(unit.source)
+        last_kept = kept_rank - 1
+
         def accumulate(r_expr: str) -> None:
             names = self._unravel(r_expr, unit.reduced, "r", body)
             env2: dict = {}
@@ -410,6 +506,40 @@ class _Emitter:
             body.emit(f"acc += {value}[0];")
 
         if unit.strategy == "thread":
+            # Each thread owns 8 adjacent outputs when they are adjacent in memory (column sums of a
+            # row-major matrix): one 128-bit load per row, several rows in flight.
+            if unit.vector:
+                groups = outputs // 8
+                body.emit(f"for (int64_t it = tk::first_item({base}LL); it < {unit.items}LL; it += gridDim.x) {{")
+                body.depth += 1
+                body.emit(f"const int64_t o = ((it / {parts}) * {THREADS}LL + threadIdx.x) * 8;")
+                body.emit(f"const int part = (int)(it % {parts});")
+                body.emit(f"if (o < {outputs}LL) {{")
+                body.depth += 1
+                kcoords = self._unravel("o", unit.kept, "x", body)
+                body.emit("float acc[8] = {};")
+                body.emit(f"const int64_t r_end = tk::imin((int64_t)(part + 1) * {chunk}LL, {size}LL);")
+                body.emit(f"_Pragma(\"unroll 8\") for (int64_t r = (int64_t)part * {chunk}LL; r < r_end; ++r) {{")
+                body.depth += 1
+                names = self._unravel("r", unit.reduced, "r", body)
+                value = self.value(unit.source, body, {}, "8", kcoords + names, "8", vdim=last_kept)
+                body.emit(f"_Pragma(\"unroll\") for (int j = 0; j < 8; ++j) acc[j] += {value}[j];")
+                body.depth -= 1
+                body.emit("}")
+                if unit.phase == "partial":
+                    body.emit(f"tk::st_row<8>({scratch} + ((int64_t)part * {outputs}LL + o), 8, acc);")
+                else:
+                    op, rsize = unit.root, prod(unit.reduced)
+                    scale = "acc[j]" if op.op == "sum" else f"(acc[j] / {rsize}.0f)"
+                    body.emit("float fin[8];")
+                    body.emit(f"_Pragma(\"unroll\") for (int j = 0; j < 8; ++j) fin[j] = {ROUND[op.output.dtype]}::rnd({scale});")
+                    env = {"ref:" + op.output.buffer: "fin"}
+                    self.dag(unit, body, env, "8", kcoords, "8")
+                body.depth -= 1
+                body.emit("}")
+                body.depth -= 1
+                body.emit("}")
+                return
             body.emit(f"for (int64_t it = tk::first_item({base}LL); it < {unit.items}LL; it += gridDim.x) {{")
             body.depth += 1
             body.emit(f"const int64_t o = (it / {parts}) * {THREADS}LL + threadIdx.x;")
@@ -419,7 +549,7 @@ class _Emitter:
             kcoords = self._unravel("o", unit.kept, "x", body)
             body.emit("float acc = 0.0f;")
             body.emit(f"const int64_t r_end = tk::imin((int64_t)(part + 1) * {chunk}LL, {size}LL);")
-            body.emit(f"for (int64_t r = (int64_t)part * {chunk}LL; r < r_end; ++r) {{")
+            body.emit(f"_Pragma(\"unroll 8\") for (int64_t r = (int64_t)part * {chunk}LL; r < r_end; ++r) {{")
             body.depth += 1
             accumulate("r")
             body.depth -= 1
@@ -435,7 +565,9 @@ class _Emitter:
             body.depth -= 1
             body.emit("}")
             return
-        # block strategy: one (output, part) per block iteration, all threads stride the reduced range
+        # block strategy: one (output, part) per block iteration, all threads stride the reduced range;
+        # runs of 4 consecutive reduced elements per thread when they are adjacent in memory
+        vector = unit.reduced[-1] % 4 == 0 and chunk % 4 == 0 and loads and all(a.strides[-1] in (0, 1) for a in loads)
         body.emit(f"for (int64_t it = tk::first_item({base}LL); it < {unit.items}LL; it += gridDim.x) {{")
         body.depth += 1
         body.emit(f"const int64_t o = it / {parts};")
@@ -443,11 +575,20 @@ class _Emitter:
         kcoords = self._unravel("o", unit.kept, "x", body)
         body.emit("float acc = 0.0f;")
         body.emit(f"const int64_t r_end = tk::imin((int64_t)(part + 1) * {chunk}LL, {size}LL);")
-        body.emit(f"for (int64_t r = (int64_t)part * {chunk}LL + threadIdx.x; r < r_end; r += {THREADS}) {{")
-        body.depth += 1
-        accumulate("r")
-        body.depth -= 1
-        body.emit("}")
+        if vector:
+            body.emit(f"_Pragma(\"unroll 8\") for (int64_t r = (int64_t)part * {chunk}LL + threadIdx.x * 4; r < r_end; r += {THREADS * 4}) {{")
+            body.depth += 1
+            names = self._unravel("r", unit.reduced, "r", body)
+            value = self.value(unit.source, body, {}, "4", kcoords + names, "4")
+            body.emit(f"acc += ({value}[0] + {value}[1]) + ({value}[2] + {value}[3]);")
+            body.depth -= 1
+            body.emit("}")
+        else:
+            body.emit(f"_Pragma(\"unroll 4\") for (int64_t r = (int64_t)part * {chunk}LL + threadIdx.x; r < r_end; r += {THREADS}) {{")
+            body.depth += 1
+            accumulate("r")
+            body.depth -= 1
+            body.emit("}")
         body.emit("acc = tk::block_sum(c, acc);")
         body.emit("if (threadIdx.x == 0) {")
         body.depth += 1
@@ -516,11 +657,15 @@ class _Emitter:
         ]
         if self.needs_simt:
             entry.append("    __shared__ tk::SimtSmem simt;")
+        if plan.uses_tc:
+            entry.append("    __shared__ tk::EpiStage epi_stage;")
         entry += [
             "    tk::Ctx c;",
             "    tk::ctx_init2(c, P.sync, P.status, P.timeout_ns, P.arrivals, &shared_state, dyn_smem);" if plan.two_cta else
             f"    tk::ctx_init(c, P.sync, P.status, P.timeout_ns, P.arrivals, &shared_state, dyn_smem, {use_tc});",
         ]
+        if plan.uses_tc:
+            entry.append("    c.epi = &epi_stage.t[0][0][0];")
         if stage_stamps:
             entry.append("    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[0] = tk::global_timer_ns();")
         tail = []

@@ -134,6 +134,7 @@ struct Ctx {
     uint32_t arrivals;     // blocks the grid barrier waits for (gridDim.x unless a test overrides it)
     SharedState* sh;
     uint8_t* slots;        // 1024-byte aligned pipeline slots
+    float* epi;            // EpiStage: one 32 x 32 FP32 transpose buffer per epilogue warp
     uint32_t stage_id;
     // pipeline cursors; each role advances its own copy through the same tile sequence
     uint32_t slot, slot_phase;     // smem ring position and parity
@@ -176,7 +177,7 @@ __device__ __forceinline__ void ctx_init(Ctx& c, uint32_t* sync, uint32_t* statu
     c.sync = sync; c.status = status; c.timeout_ns = timeout_ns; c.sh = sh;
     c.arrivals = arrivals ? arrivals : gridDim.x;
     c.slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
-    c.stage_id = 0; c.slot = 0; c.slot_phase = 0; c.acc = 0; c.acc_phase = 0; c.tmem = 0;
+    c.stage_id = 0; c.slot = 0; c.slot_phase = 0; c.acc = 0; c.acc_phase = 0; c.tmem = 0; c.epi = nullptr;
     c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         sh->abort = 0;
@@ -257,6 +258,14 @@ __device__ __forceinline__ void from_f32(__nv_bfloat16* p, float x) { *p = __flo
 __device__ __forceinline__ void from_f32(__half* p, float x) { *p = __float2half_rn(x); }
 
 __device__ __forceinline__ int64_t imin(int64_t a, int64_t b) { return a < b ? a : b; }
+__device__ __forceinline__ int64_t imax(int64_t a, int64_t b) { return a > b ? a : b; }
+// Pull `bytes` starting at p into L2 (one request per 128-byte line); used by epilogue warps to fetch the
+// operands of the NEXT tile's epilogue while that tile's MMAs are still running.
+__device__ __forceinline__ void prefetch_l2(const void* p, int bytes) {
+    const char* q = reinterpret_cast<const char*>(reinterpret_cast<uintptr_t>(p) & ~uintptr_t(127));
+    const char* end = reinterpret_cast<const char*>(p) + bytes;
+    for (; q < end; q += 128) asm volatile("prefetch.global.L2 [%0];" :: "l"(q));
+}
 __device__ __forceinline__ float relu(float x) { return x < 0.0f ? 0.0f : x; }   // keeps NaN like torch.relu
 
 // W consecutive elements starting at p -> FP32.  Vector loads when p is 16-byte aligned and all W are valid.
@@ -365,6 +374,47 @@ __device__ __forceinline__ void st_row16(T16* p, int nvalid, const float* v) {
 template <int W> __device__ __forceinline__ void st_row(__nv_bfloat16* p, int nvalid, const float* v) { st_row16<W>(p, nvalid, v); }
 template <int W> __device__ __forceinline__ void st_row(__half* p, int nvalid, const float* v) { st_row16<W>(p, nvalid, v); }
 
+// Streaming variants for data touched exactly once by the kernel (FP32 masters read by the SGD
+// expression, FP32 gradients and updated state written by it): the .cs policy marks the lines
+// evict-first so they do not push GEMM operands out of L2.
+__device__ __forceinline__ float4 ldg_stream(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.cs.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void stg_stream(float4* p, float4 v) {
+    asm volatile("st.global.cs.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+template <int W>
+__device__ __forceinline__ void ld_row_stream(const float* p, int64_t step, int nvalid, float* out) {
+    if constexpr (W % 4 == 0) {
+        if (step == 1 && nvalid >= W && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < W; j += 4) {
+                const float4 v = ldg_stream(reinterpret_cast<const float4*>(p + j));
+                out[j] = v.x; out[j + 1] = v.y; out[j + 2] = v.z; out[j + 3] = v.w;
+            }
+            return;
+        }
+    }
+    ld_row_strided<W>(p, step, nvalid, out);
+}
+template <int W, typename T16>
+__device__ __forceinline__ void ld_row_stream(const T16* p, int64_t step, int nvalid, float* out) { ld_row_strided<W>(p, step, nvalid, out); }
+template <int W>
+__device__ __forceinline__ void st_row_stream(float* p, int nvalid, const float* v) {
+    if constexpr (W % 4 == 0) {
+        if (nvalid >= W && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < W; j += 4) stg_stream(reinterpret_cast<float4*>(p + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+            return;
+        }
+    }
+    st_row<W>(p, nvalid, v);
+}
+template <int W, typename T16>
+__device__ __forceinline__ void st_row_stream(T16* p, int nvalid, const float* v) { st_row<W>(p, nvalid, v); }
+
 // Block-wide FP32 sum; the total is valid in thread 0.  All threads of the block must call it.
 __device__ __forceinline__ float block_sum(Ctx& c, float v) {
 #pragma unroll
@@ -399,6 +449,47 @@ __device__ __forceinline__ void tile_coords(int64_t t, int tiles_m, int tiles_n,
     const int within = static_cast<int>(t - static_cast<int64_t>(group) * per_group);
     tm = first + within % rows;
     tn = within / rows;
+}
+
+// ----------------------------------------------------------------------------
+// Epilogue chunk.  tcgen05.ld hands every lane one accumulator ROW (32 consecutive columns), so a
+// warp-wide global access would touch 32 different rows.  The chunk is therefore transposed through
+// a padded shared-memory buffer: afterwards 8 (or 4) lanes share a row and each warp-wide 128-bit
+// access covers whole 128-byte (or 64-byte) row segments.  All rows' loads are issued before the
+// first store (Epi::run_rows).
+// ----------------------------------------------------------------------------
+constexpr int kEpiPitch = 36;                       // floats per staged row: 16-byte aligned, conflict-free
+struct alignas(16) EpiStage { float t[kEpiThreads / 32][32][kEpiPitch]; };
+
+template <typename Epi, typename Params>
+__device__ __forceinline__ void epilogue_chunk(Ctx& c, const Params& P, const float* acc, int row0, int col0, int ncols) {
+    float* stage = c.epi + (c.warp - 2) * 32 * kEpiPitch;
+    float* mine = stage + c.lane * kEpiPitch;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(mine + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+    __syncwarp();
+    if constexpr (Epi::kWide) {
+        const int cq = (c.lane & 7) * 4, rq = c.lane >> 3;      // runs of 4 columns, rows rq, rq+4, ...
+        float v[8][4];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const float4 q = *reinterpret_cast<const float4*>(stage + (rq + 4 * r) * kEpiPitch + cq);
+            v[r][0] = q.x; v[r][1] = q.y; v[r][2] = q.z; v[r][3] = q.w;
+        }
+        Epi::template run_rows<8, 4>(P, row0 + rq, 4, col0 + cq, max(0, min(4, ncols - cq)), v);
+    } else {
+        const int cq = (c.lane & 3) * 8, rq = c.lane >> 2;      // runs of 8 columns, rows rq, rq+8, ...
+        float v[4][8];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const float4 q0 = *reinterpret_cast<const float4*>(stage + (rq + 8 * r) * kEpiPitch + cq);
+            const float4 q1 = *reinterpret_cast<const float4*>(stage + (rq + 8 * r) * kEpiPitch + cq + 4);
+            v[r][0] = q0.x; v[r][1] = q0.y; v[r][2] = q0.z; v[r][3] = q0.w;
+            v[r][4] = q1.x; v[r][5] = q1.y; v[r][6] = q1.z; v[r][7] = q1.w;
+        }
+        Epi::template run_rows<4, 8>(P, row0 + rq, 8, col0 + cq, max(0, min(8, ncols - cq)), v);
+    }
+    __syncwarp();
 }
 
 // ----------------------------------------------------------------------------
@@ -479,9 +570,14 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
         const int quarter = c.warp & 3;                // TMEM lanes this warp may read
         for (int64_t t = first_item(item_base); t < tiles && !c.aborted(); t += step) {
             int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+            if (t + step < tiles) {
+                int pm, pn; tile_coords(t + step, tiles_m, tiles_n, pm, pn);
+                const int prow = pm * BM + quarter * 32 + c.lane;
+                if (prow < M && pn * BN < N) Epi::prefetch(P, prow, pn * BN, min(BN, N - pn * BN));
+            }
             if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
             tc_fence_after();
-            const int row = tm * BM + quarter * 32 + c.lane;
+            const int row0 = tm * BM + quarter * 32;
             const uint32_t taddr = c.tmem + c.acc * kMaxBN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
             for (int cc = 0; cc < BN; cc += 32) {
@@ -490,7 +586,7 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
                 float acc[32];
                 tc_ld32(taddr + cc, acc);
                 tc_wait_ld();
-                if (row < M) Epi::template run<32>(P, row, col0, min(32, N - col0), acc);
+                epilogue_chunk<Epi>(c, P, acc, row0, col0, min(32, N - col0));
             }
             tc_fence_before();
             __syncwarp();

@@ -50,7 +50,7 @@ __device__ __forceinline__ void ctx_init2(Ctx& c, uint32_t* sync, uint32_t* stat
     c.sync = sync; c.status = status; c.timeout_ns = timeout_ns; c.sh = sh;
     c.arrivals = arrivals ? arrivals : gridDim.x;
     c.slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
-    c.stage_id = 0; c.slot = 0; c.slot_phase = 0; c.acc = 0; c.acc_phase = 0; c.tmem = 0;
+    c.stage_id = 0; c.slot = 0; c.slot_phase = 0; c.acc = 0; c.acc_phase = 0; c.tmem = 0; c.epi = nullptr;
     c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         sh->abort = 0;
@@ -173,9 +173,14 @@ __device__ __forceinline__ void gemm_tc2(Ctx& c, const Params& P, const CUtensor
         const int quarter = c.warp & 3;
         for (int64_t t = first; t < tiles && !c.aborted(); t += clusters) {
             int tm, tn; pair_coords<GROUP>(t, tiles_m, tiles_n, tm, tn);
+            if (t + clusters < tiles) {
+                int pm, pn; pair_coords<GROUP>(t + clusters, tiles_m, tiles_n, pm, pn);
+                const int prow = pm * TM + static_cast<int>(rank) * 128 + quarter * 32 + c.lane;
+                if (prow < M && pn * TN < N) Epi::prefetch(P, prow, pn * TN, min(TN, N - pn * TN));
+            }
             if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
             tc_fence_after();
-            const int row = tm * TM + static_cast<int>(rank) * 128 + quarter * 32 + c.lane;
+            const int row0 = tm * TM + static_cast<int>(rank) * 128 + quarter * 32;
             const uint32_t taddr = c.tmem + c.acc * kMaxBN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
             for (int cc = 0; cc < TN; cc += 32) {
@@ -184,7 +189,7 @@ __device__ __forceinline__ void gemm_tc2(Ctx& c, const Params& P, const CUtensor
                 float acc[32];
                 tc_ld32(taddr + cc, acc);
                 tc_wait_ld();
-                if (row < M) Epi::template run<32>(P, row, col0, min(32, N - col0), acc);
+                epilogue_chunk<Epi>(c, P, acc, row0, col0, min(32, N - col0));
             }
             tc_fence_before();
             __syncwarp();

@@ -111,11 +111,25 @@ class Unit:
     parts: int = 1
     phase: str = ""                        # "" | "partial" | "finish"
     scratch: str = ""                      # partial-sum buffer name
+    vector: bool = False                   # thread strategy: 8 adjacent outputs per thread
     items: int = 1
 
     @property
     def writes(self) -> set[str]:
         return {s.buffer for s in self.stores}
+
+
+def point_unroll(total: int) -> int:
+    """Independent 8-element chunks each thread of a flat pointwise unit keeps in flight per iteration.
+
+    Large streams need ~48 KiB in flight per SM to cover HBM latency (8 chunks x 192 threads x 32 B);
+    small ones keep more blocks busy with less unrolling.
+    """
+    if total >= SM_COUNT * THREADS * 8 * 8:
+        return 8
+    if total >= SM_COUNT * THREADS * 8 * 2:
+        return 2
+    return 1
 
 
 class _Materialize(Exception):
@@ -751,7 +765,9 @@ class Planner:
                 inner_kept = bool(unit_strides) and unit_strides[-1] < kept_rank
             if outputs >= 32 and (inner_kept or size <= 128):
                 unit.strategy = "thread"
-                blocks = -(-outputs // THREADS)
+                unit.vector = bool(unit.kept[-1] % 8 == 0 and outputs >= 8 * THREADS and loads
+                                   and all(a.strides[kept_rank - 1] in (0, 1) for a in loads))
+                blocks = -(-outputs // (THREADS * 8 if unit.vector else THREADS))
                 parts = min(max(1, SM_COUNT // blocks), max(1, size // 64), 64)
             else:
                 unit.strategy = "block"
@@ -764,7 +780,7 @@ class Planner:
             dtypes[scratch], shapes[scratch] = "float32", (parts, outputs)
             partial = Unit("reduce", unit.name + "_partial", unit.index, unit.dims, root=unit.root, kept=unit.kept,
                            reduced=unit.reduced, source=unit.source, strategy=unit.strategy, parts=parts, phase="partial",
-                           scratch=scratch)
+                           scratch=scratch, vector=unit.vector)
             partial.stores.append(Store(scratch, "float32"))
             self._collect_reads(partial)
             unit.phase, unit.scratch = "finish", scratch
@@ -798,8 +814,9 @@ class Planner:
             if unit.phase == "finish":
                 unit.items = -(-outputs // THREADS)
             elif unit.strategy == "thread":
-                unit.items = -(-outputs // THREADS) * unit.parts
+                unit.items = -(-outputs // (THREADS * 8 if unit.vector else THREADS)) * unit.parts
             else:
                 unit.items = outputs * unit.parts
         else:
-            unit.items = max(1, -(-prod(unit.dims) // (THREADS * 8)))
+            total = prod(unit.dims)
+            unit.items = max(1, -(-total // (THREADS * 8 * point_unroll(total))))
