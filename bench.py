@@ -8,7 +8,7 @@ A step is one forward + loss + backward + FP32-master SGD pass of the medium MLP
 resident synthetic batch.  At N = 1 the whole step is ONE generated sm_100a
 kernel replayed from a CUDA graph.  At N > 1 the batch is split evenly over the
 ranks (strong scaling); each rank replays gradient kernel -> NCCL all-reduce of
-the FP32 gradients -> update kernel.  Exactly K steps are timed with CUDA
+the BF16 gradients -> update kernel.  Exactly K steps are timed with CUDA
 events between barrier + synchronize pairs and the maximum over ranks is
 reported.  One JSON line is printed by rank 0.
 """
@@ -67,10 +67,10 @@ def kernel_sources() -> dict[str, str]:
     sources = {"medium_n1": codegen.generate(_medium_program(MEDIUM_BATCH),
                                              inplace_outputs={1 + count + i: i for i in range(count)}).source}
     for world in (2, 4, 8):
-        gradient, update = split_at_gradients(_medium_program(MEDIUM_BATCH // world), count)
+        gradient, update = split_at_gradients(_medium_program(MEDIUM_BATCH // world), count, narrow_exchange=True)
         sources[f"medium_grad_n{world}"] = codegen.generate(gradient).source
         if world == 2:
-            sources["medium_update"] = codegen.generate(update, inplace_outputs={i: i for i in range(count)}).source
+            sources["medium_update"] = codegen.generate(update, inplace_outputs={count + i: i for i in range(count)}).source
     return sources
 
 
@@ -339,7 +339,7 @@ def main() -> None:
         torch.cuda.synchronize()
         a.record()
         for _ in range(5):
-            step.gradient.module.launch(flat, step.views, step.gradient_workspace, stream)
+            step.gradient.module.launch(flat, (step.loss, *step.views), step.gradient_workspace, stream)
         b.record()
         b.synchronize()
         kernel_ms = a.elapsed_time(b) / 5
@@ -362,7 +362,7 @@ def main() -> None:
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload} medium MLP {'-'.join(map(str, MEDIUM_SIZES))}, global batch {MEDIUM_BATCH}, BF16 compute / FP32 master, SGD lr 1e-3",
                    "global_batch": MEDIUM_BATCH, "rows_per_rank": work.batch, "resident_batches": len(work.batches),
-                   "parallelism": f"dp{world} (batch-sharded, NCCL all-reduce of FP32 gradients)" if world > 1 else "single GPU, one kernel per step",
+                   "parallelism": f"dp{world} (batch-sharded, NCCL all-reduce of the BF16 gradients)" if world > 1 else "single GPU, one kernel per step",
                    "l2": "inputs larger than L2 (FP32 weights %d MB, %d MB per batch)" % (work.weight_elements * 4 // 2**20, work.batch * (MEDIUM_SIZES[0] + MEDIUM_SIZES[-1]) * 2 // 2**20),
                    "graph_steps": 0 if args.eager else steps},
         "latency_us": {"p50": round(statistics.median(samples), 1), "min": round(min(samples), 1), "max": round(max(samples), 1),

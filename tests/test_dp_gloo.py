@@ -14,6 +14,7 @@ from trainkernel_b200.dp import shard_rows
 from trainkernel_b200.passes import split_at_gradients
 
 SIZES, BATCH, WORLD = (32, 64, 32), 16, 2
+NARROW = True      # exchange the BF16 values the FP32 gradients are widened from
 
 
 def _free_port() -> int:
@@ -30,15 +31,17 @@ def _rank_main(rank: int, port: int, results):
         n = len(work.state)
         x, t = work.batches[0]
         program, _ = tk.capture(work.fn(), (work.state, x, t))
-        gradient_half, update_half = split_at_gradients(program, n)
+        gradient_half, update_half = split_at_gradients(program, n, narrow_exchange=NARROW)
         state = work.state
         for step in range(3):
             x, t = work.batches[step % len(work.batches)]
             outputs = [o.clone() for o in interpreter.run(gradient_half, (*state, x, t))]
-            for tensor in outputs:                      # loss and gradients: average over ranks
-                dist.all_reduce(tensor, op=dist.ReduceOp.SUM)
-                tensor /= WORLD
-            state = tuple(o.clone() for o in interpreter.run(update_half, (*state, *outputs[1:])))
+            for i, tensor in enumerate(outputs):        # loss and gradients: average over ranks
+                wide = tensor.float()                   # gloo has no BF16 average; round back afterwards
+                dist.all_reduce(wide, op=dist.ReduceOp.SUM)
+                outputs[i] = (wide / WORLD).to(tensor.dtype)
+            updated = interpreter.run(update_half, (*state, *outputs[1:]))
+            state = tuple(o.clone() for o in updated[-n:])
         gathered = [None] * WORLD
         dist.all_gather_object(gathered, [p.numpy().copy() for p in state])
         if rank == 0:

@@ -123,3 +123,22 @@ def test_barrier_timeout_is_reported_not_hung():
     out = compiled(fresh, inputs[1], inputs[2])
     assert runner.status()[0] == 0
     assert bool(torch.isfinite(out[0]))
+
+
+@pytest.mark.parametrize("exchange", ["narrow", "float32"])
+def test_split_step_without_a_process_group_matches_oracle(exchange):
+    """Gradient kernel + update kernel (the data-parallel form, world size 1) equals the one-kernel step."""
+    from trainkernel_b200 import dp, workloads
+    import trainkernel_b200 as tk
+    work = workloads.build("c2", seed=1, device="cuda")
+    cpu = workloads.build("c2", seed=1, device="cpu")
+    x, t = work.batches[0]
+    step = dp.ShardedTrainingStep(work.fn(), (work.state, x, t), exchange=exchange)
+    assert step.narrow == (exchange == "narrow")
+    program, _ = tk.capture(cpu.fn(), (cpu.state, *cpu.batches[0]))
+    expected = oracle_outputs(program, (cpu.state, *cpu.batches[0]))
+    pointers = [p.data_ptr() for p in work.state]
+    loss, grads, state = step(work.state, x, t)
+    step.status()
+    assert_outputs_close((loss, grads, state), expected, 2e-2, "split step")
+    assert [p.data_ptr() for p in state] == pointers

@@ -361,7 +361,7 @@ class _Emitter:
                       f"{self.pointer(b.buffer, b.dtype, True)} + {b.offset}LL, {ld}LL, {n}, {k}, {base}LL);")
         else:
             self.needs_simt = True
-            body.emit(f"tk::gemm_simt<{CTYPE[a.dtype]}, {ROUND[a.round_to]}, {CTYPE[b.dtype]}, {ROUND[b.round_to]}, {epi}>(c, P, &simt, "
+            body.emit(f"tk::gemm_simt<{CTYPE[a.dtype]}, {ROUND[a.round_to]}, {CTYPE[b.dtype]}, {ROUND[b.round_to]}, {epi}>(c, P, reinterpret_cast<tk::SimtSmem*>(c.slots), "
                       f"{self.pointer(a.buffer, a.dtype, True)} + {a.offset}LL, {a.strides[0]}LL, {a.strides[1]}LL, "
                       f"{self.pointer(b.buffer, b.dtype, True)} + {b.offset}LL, {b.strides[0]}LL, {b.strides[1]}LL, {m}, {n}, {k}, {base}LL);")
 
@@ -633,6 +633,7 @@ class _Emitter:
         n_in = max(1, len(plan.program.inputs))
         n_out = max(1, len(plan.program.outputs))
         n_maps = max(1, len(self.maps))
+        n_maps_used = len(self.maps)
         use_tc = "true" if plan.uses_tc else "false"
         header = [
             '#include "tk_gemm_2cta.cuh"' if plan.two_cta else '#include "tk_device.cuh"',
@@ -655,8 +656,6 @@ class _Emitter:
             "    extern __shared__ uint8_t dyn_smem[];",
             "    __shared__ tk::SharedState shared_state;",
         ]
-        if self.needs_simt:
-            entry.append("    __shared__ tk::SimtSmem simt;")
         if plan.uses_tc:
             entry.append("    __shared__ tk::EpiStage epi_stage;")
         entry += [
@@ -666,6 +665,8 @@ class _Emitter:
         ]
         if plan.uses_tc:
             entry.append("    c.epi = &epi_stage.t[0][0][0];")
+        if n_maps_used:
+            entry.append(f"    if (threadIdx.x < {n_maps_used}) tk::tma_prefetch_desc(&P.maps[threadIdx.x]);")
         if stage_stamps:
             entry.append("    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[0] = tk::global_timer_ns();")
         tail = []
@@ -769,6 +770,8 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     materialized = sum((1 if u.root is not None and u.phase != "partial" else 0) + len(u.members) for u in plan.units)
     from .plan import SM_COUNT  # noqa: F401
     dyn = 0
+    if emitter.needs_simt:
+        dyn = 4 * (32 * 129 + 4 + 128 * 36) + 1024          # tk::SimtSmem + alignment slack
     if plan.uses_tc:
         dyn = 4 * (128 * 64 * 2 + 256 * 64 * 2) + 1024
     return GeneratedKernel(

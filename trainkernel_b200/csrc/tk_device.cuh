@@ -600,9 +600,11 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
 // SIMT GEMM unit (exact FP32 accumulation with fmaf, sequential in K per output).
 // Operands are read through arbitrary element strides and converted to FP32, optionally
 // re-rounded to a 16-bit type first (a cast folded into the load).  32x32 output tile per
-// block-iteration, 128 compute threads each owning a 2x4 strip.
+// block-iteration, 128 compute threads each owning a 2x4 strip.  The staging buffers live at the
+// start of the dynamic shared memory (idle whenever all threads of a block are inside this unit).
 // ----------------------------------------------------------------------------
-struct alignas(16) SimtSmem { float a[32][33]; float pad[4]; float b[32][36]; };
+constexpr int kSimtK = 128;            // K depth staged per step: few steps, many loads in flight per step
+struct alignas(16) SimtSmem { float a[32][kSimtK + 1]; float pad[4 - (32 * (kSimtK + 1)) % 4]; float b[kSimtK][36]; };
 
 template <typename TA, typename RA, typename TB, typename RB, typename Epi, typename Params>
 __device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm, const TA* A, int64_t a_rs, int64_t a_ks,
@@ -611,26 +613,40 @@ __device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm,
     const int64_t tiles = static_cast<int64_t>((M + 31) / 32) * tiles_n;
     const int tid = threadIdx.x;
     const int ty = tid / 8, tx = tid % 8;      // valid for tid < 128: rows 2*ty.., cols 4*tx..
+    const bool a_k_fast = a_ks <= a_rs, b_n_fast = b_cs <= b_ks;
     for (int64_t t = first_item(item_base); t < tiles; t += gridDim.x) {
         const int row0 = static_cast<int>(t / tiles_n) * 32, col0 = static_cast<int>(t % tiles_n) * 32;
         float acc[2][4] = {};
-        for (int k0 = 0; k0 < K; k0 += 32) {
+        for (int k0 = 0; k0 < K; k0 += kSimtK) {
+            const int depth = min(kSimtK, K - k0);
             __syncthreads();
-            for (int p = tid; p < 1024; p += kThreads) {
-                // A tile: consecutive threads walk K when K is the unit-stride axis, rows otherwise.
-                int ar, ak;
-                if (a_ks <= a_rs) { ar = p / 32; ak = p % 32; } else { ar = p % 32; ak = p / 32; }
-                const int gr = row0 + ar, gk = k0 + ak;
-                sm->a[ar][ak] = (gr < M && gk < K) ? RA::rnd(to_f32(A[gr * a_rs + gk * a_ks])) : 0.0f;
-                int bk, bc;
-                if (b_cs <= b_ks) { bk = p / 32; bc = p % 32; } else { bk = p % 32; bc = p / 32; }
-                const int gk2 = k0 + bk, gc = col0 + bc;
-                sm->b[bk][bc] = (gk2 < K && gc < N) ? RB::rnd(to_f32(B[gk2 * b_ks + gc * b_cs])) : 0.0f;
+            // Stage A[32, depth] and B[depth, 32]; eight independent loads per thread are issued
+            // before the first shared-memory store so their latencies overlap.
+            for (int p0 = tid; p0 < 32 * depth; p0 += kThreads * 8) {
+                float va[8], vb[8];
+                int ia[8], ib[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int p = p0 + u * kThreads;
+                    const bool live = p < 32 * depth;
+                    // consecutive threads walk the unit-stride axis of each operand
+                    const int ar = a_k_fast ? p / depth : p % 32, ak = a_k_fast ? p % depth : p / 32;
+                    const int bk = b_n_fast ? p / 32 : p % depth, bc = b_n_fast ? p % 32 : p / depth;
+                    ia[u] = live ? ar * (kSimtK + 1) + ak : -1;
+                    ib[u] = live ? bk * 36 + bc : -1;
+                    const int gr = row0 + ar, gc = col0 + bc;
+                    va[u] = (live && gr < M) ? RA::rnd(to_f32(A[static_cast<int64_t>(gr) * a_rs + static_cast<int64_t>(k0 + ak) * a_ks])) : 0.0f;
+                    vb[u] = (live && gc < N) ? RB::rnd(to_f32(B[static_cast<int64_t>(k0 + bk) * b_ks + static_cast<int64_t>(gc) * b_cs])) : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (ia[u] >= 0) { (&sm->a[0][0])[ia[u]] = va[u]; (&sm->b[0][0])[ib[u]] = vb[u]; }
+                }
             }
             __syncthreads();
             if (tid < 128) {
 #pragma unroll 8
-                for (int k = 0; k < 32; ++k) {
+                for (int k = 0; k < depth; ++k) {
                     const float a0 = sm->a[2 * ty][k], a1 = sm->a[2 * ty + 1][k];
                     const float4 b = *reinterpret_cast<const float4*>(&sm->b[k][4 * tx]);
                     acc[0][0] = fmaf(a0, b.x, acc[0][0]); acc[0][1] = fmaf(a0, b.y, acc[0][1]);

@@ -9,8 +9,12 @@ each rank's loss is a mean over its own rows and shards are equal-sized, the
 average of the local gradients is the full-batch gradient.
 
 `reduce="nccl"` launches the two halves as separate kernels with one
-`torch.distributed.all_reduce(AVG)` over a flat gradient buffer between them
-(a CUDA-graph-capturable sequence on one stream).
+`torch.distributed.all_reduce(AVG)` over a flat gradient buffer (plus one over
+the scalar loss) between them — a CUDA-graph-capturable sequence on one stream.
+When the FP32 gradients are widenings of BF16 values, which is what a
+BF16-compute step produces, the BF16 values are what is exchanged
+(`exchange="narrow"`): half the bytes, and the averaged gradient is rounded to
+BF16 once more, as the full-batch step rounds its own gradient.
 """
 from __future__ import annotations
 
@@ -43,9 +47,11 @@ class ShardedTrainingStep:
     """
 
     def __init__(self, fn: Callable[..., Any], example_inputs: Sequence[Any], *, group: Any = None,
-                 reduce: str = "nccl", **options: Any) -> None:
+                 reduce: str = "nccl", exchange: str = "auto", **options: Any) -> None:
         if reduce != "nccl":
             raise ValueError("trainkernel: reduce must be 'nccl'")
+        if exchange not in ("auto", "float32", "narrow"):
+            raise ValueError("trainkernel: exchange must be 'auto', 'float32' or 'narrow'")
         if "inplace_outputs" in options:
             raise ValueError("trainkernel: the sharded step derives its own state mapping")
         self.group = group
@@ -55,23 +61,43 @@ class ShardedTrainingStep:
         n = self.count = len(state_leaves)
         self.output_tree = output_tree
         self.program = program
-        gradient_half, update_half = split_at_gradients(program, n)
+        # "narrow": exchange the 16-bit values the FP32 gradients are widened from (half the bytes).
+        self.narrow = False
+        if exchange in ("auto", "narrow"):
+            try:
+                gradient_half, update_half = split_at_gradients(program, n, narrow_exchange=True)
+                self.narrow = True
+            except ValueError:
+                if exchange == "narrow":
+                    raise
+        if not self.narrow:
+            gradient_half, update_half = split_at_gradients(program, n)
         self.gradient = runtime.compile_program(gradient_half, flat, **options)
         device = self.device = self.gradient.device
-        # loss and every gradient live back to back in one FP32 buffer so a single collective covers them
-        sizes = [1] + [spec_numel(s.shape) for s in gradient_half.outputs[1:]]
-        for spec in gradient_half.outputs:
-            if spec.dtype != "float32":
-                raise ValueError("trainkernel: the sharded step exchanges FP32 losses and gradients")
-        padded = [-(-size // 64) * 64 for size in sizes]          # keep every slice 256-byte aligned
-        self.flat = torch.zeros(sum(padded), dtype=torch.float32, device=device)
+        # The loss is one FP32 word; every exchanged gradient lives back to back in one flat buffer
+        # of the exchange dtype, so one collective covers them all.
+        exchanged = gradient_half.outputs[1:]
+        dtypes = {spec.dtype for spec in exchanged}
+        if len(dtypes) != 1 or gradient_half.outputs[0].dtype != "float32":
+            raise ValueError("trainkernel: the sharded step needs an FP32 loss and gradients of one dtype")
+        dtype = getattr(torch, dtypes.pop())
+        sizes = [spec_numel(spec.shape) for spec in exchanged]
+        padded = [-(-size // 128) * 128 for size in sizes]          # keep every slice 256-byte aligned
+        self.loss = torch.zeros((), dtype=torch.float32, device=device)
+        self.flat = torch.zeros(sum(padded), dtype=dtype, device=device)
         self.views = []
         cursor = 0
-        for spec, size, pad in zip(gradient_half.outputs, sizes, padded):
+        for spec, size, pad in zip(exchanged, sizes, padded):
             self.views.append(self.flat[cursor:cursor + size].view(spec.shape))
             cursor += pad
-        update_inputs = tuple(state_leaves) + tuple(self.views[1:])
-        self.update = runtime.compile_program(update_half, update_inputs, inplace_outputs={i: i for i in range(n)}, **options)
+        update_inputs = tuple(state_leaves) + tuple(self.views)
+        offset = n if self.narrow else 0                              # narrow: outputs are (grads..., updated...)
+        self.update = runtime.compile_program(update_half, update_inputs,
+                                              inplace_outputs={offset + i: i for i in range(n)}, **options)
+        self.gradients = None
+        if self.narrow:
+            self.gradients = tuple(torch.empty(spec.shape, dtype=getattr(torch, spec.dtype), device=device)
+                                   for spec in update_half.outputs[:n])
         self.gradient_workspace = torch.empty(self.gradient.generated.workspace_elements, dtype=torch.float32, device=device)
         self.update_workspace = torch.empty(self.update.generated.workspace_elements, dtype=torch.float32, device=device)
 
@@ -87,12 +113,19 @@ class ShardedTrainingStep:
         self.gradient._validate_inputs(flat)
         state = flat[:self.count]
         stream = torch.cuda.current_stream(self.device).cuda_stream
-        self.gradient.module.launch(flat, self.views, self.gradient_workspace, stream)
+        self.gradient.module.launch(flat, (self.loss, *self.views), self.gradient_workspace, stream)
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
             dist.all_reduce(self.flat, op=dist.ReduceOp.AVG, group=self.group)
-        self.update.module.launch(state + tuple(self.views[1:]), state, self.update_workspace, stream)
+            dist.all_reduce(self.loss, op=dist.ReduceOp.AVG, group=self.group)
+        if self.narrow:
+            outputs = (*self.gradients, *state)
+            grads = self.gradients
+        else:
+            outputs = state
+            grads = tuple(self.views)
+        self.update.module.launch(state + tuple(self.views), outputs, self.update_workspace, stream)
         torch.autograd.graph.increment_version(list(state))
-        return tree_unflatten([self.views[0], *self.views[1:], *state], self.output_tree)
+        return tree_unflatten([self.loss, *grads, *state], self.output_tree)
 
     def status(self) -> None:
         self.gradient.status()

@@ -88,8 +88,14 @@ def canonicalize_transposed_mm(program: Program) -> Program:
     return Program(program.inputs, tuple(rewritten), tuple(relayout(value) for value in program.outputs))
 
 
-def split_at_gradients(program: Program, state_count: int) -> tuple[Program, Program]:
+def split_at_gradients(program: Program, state_count: int, *, narrow_exchange: bool = False) -> tuple[Program, Program]:
     """Cut a training program into a gradient half and an update half.
+
+    With `narrow_exchange=True` a gradient that is merely the FP32 widening of a 16-bit value
+    (the usual BF16-compute / FP32-master step) is cut one operation earlier, at the 16-bit
+    value: the gradient half then returns `(loss, narrow grads...)`, and the update half takes
+    `(state..., narrow grads...)` and returns `(grads..., updated...)`.  Half as many bytes cross
+    the cut, which is what a cross-rank exchange pays for.
 
     `program` follows the `compile_training` contract: inputs start with
     `state_count` state leaves and outputs are `(loss, grads..., updated...)`.
@@ -105,6 +111,8 @@ def split_at_gradients(program: Program, state_count: int) -> tuple[Program, Pro
     grad_specs = program.outputs[1:1 + n]
     update_specs = program.outputs[1 + n:]
     input_buffers = {spec.buffer for spec in program.inputs}
+    if narrow_exchange:
+        return _split_narrow(program, n)
     for spec in grad_specs:
         if spec.buffer in input_buffers or spec.offset or spec.strides != row_major(spec.shape):
             raise ValueError("trainkernel: gradients must be computed dense values to be exchanged")
@@ -146,4 +154,52 @@ def split_at_gradients(program: Program, state_count: int) -> tuple[Program, Pro
             raise ValueError("trainkernel: loss or gradient depends on the update half")
     gradient_half = Program(program.inputs, tuple(first), program.outputs[:1 + n])
     update_half = Program(tuple(state_inputs) + grad_inputs, tuple(later), tuple(update_specs))
+    return gradient_half, update_half
+
+
+def _split_narrow(program: Program, n: int) -> tuple[Program, Program]:
+    """`split_at_gradients` with the cut moved below the widening cast of each gradient."""
+    producer = {op.output.buffer: op for op in program.operations}
+    input_buffers = {spec.buffer for spec in program.inputs}
+    cuts: list[TensorSpec] = []
+    for spec in program.outputs[1:1 + n]:
+        op = producer.get(spec.buffer)
+        source = op.inputs[0] if op is not None and op.op == "cast" and op.inputs else None
+        narrow = (isinstance(source, TensorSpec) and source.buffer in producer and source.dtype in ("bfloat16", "float16")
+                  and spec.dtype == "float32" and spec.offset == 0 and spec.strides == row_major(spec.shape))
+        if not narrow:
+            raise ValueError("trainkernel: narrow exchange needs gradients that are FP32 casts of 16-bit values")
+        cuts.append(producer[source.buffer].output)
+    cut_buffers = [spec.buffer for spec in cuts]
+    if len(set(cut_buffers)) != n:
+        raise ValueError("trainkernel: gradient outputs must be distinct values")
+    dependent: set[str] = set(cut_buffers)
+    later: list[Operation] = []
+    for op in program.operations:
+        if op.output.buffer in dependent:
+            continue
+        if any(isinstance(value, TensorSpec) and value.buffer in dependent for value in op.inputs):
+            dependent.add(op.output.buffer)
+            later.append(op)
+    later_outputs = {op.output.buffer for op in later}
+    needed: set[str] = {program.outputs[0].buffer, *cut_buffers}
+    first: list[Operation] = []
+    for op in reversed(program.operations):
+        if op.output.buffer in needed and op.output.buffer not in later_outputs:
+            first.append(op)
+            needed.update(value.buffer for value in op.inputs if isinstance(value, TensorSpec))
+    first.reverse()
+    if needed & later_outputs:
+        raise ValueError("trainkernel: loss or gradient depends on the update half")
+    state_inputs = program.inputs[:n]
+    allowed = {spec.buffer for spec in state_inputs} | set(cut_buffers) | later_outputs
+    for op in later:
+        for value in op.inputs:
+            if isinstance(value, TensorSpec) and value.buffer not in allowed:
+                raise ValueError(f"trainkernel: update half reads {value.buffer}, which is not state or a gradient")
+    for spec in program.outputs[1:]:
+        if spec.buffer not in later_outputs:
+            raise ValueError("trainkernel: gradients and updated state must derive from state and exchanged gradients only")
+    gradient_half = Program(program.inputs, tuple(first), (program.outputs[0], *cuts))
+    update_half = Program(tuple(state_inputs) + tuple(cuts), tuple(later), tuple(program.outputs[1:]))
     return gradient_half, update_half
