@@ -7,8 +7,10 @@ A step is one forward + loss + backward + FP32-master SGD pass of the medium MLP
 (4 layers 4096-8192-8192-8192-4096, global batch 8192, BF16 compute) over one
 resident synthetic batch.  At N = 1 the whole step is ONE generated sm_100a
 kernel replayed from a CUDA graph.  At N > 1 the batch is split evenly over the
-ranks (strong scaling); each rank replays gradient kernel -> NCCL all-reduce of
-the BF16 gradients -> update kernel.  Exactly K steps are timed with CUDA
+ranks (strong scaling); each rank still replays ONE kernel per step, which averages
+the BF16 gradients with its peers over NVLink peer memory between the backward
+GEMMs and the updates (--dp nccl selects the baseline: gradient kernel -> NCCL
+all-reduce -> update kernel).  Exactly K steps are timed with CUDA
 events between barrier + synchronize pairs and the maximum over ranks is
 reported.  One JSON line is printed by rank 0.
 """
@@ -71,6 +73,9 @@ def kernel_sources() -> dict[str, str]:
         sources[f"medium_grad_n{world}"] = codegen.generate(gradient).source
         if world == 2:
             sources["medium_update"] = codegen.generate(update, inplace_outputs={count + i: i for i in range(count)}).source
+        from trainkernel_b200.passes import insert_gradient_exchange
+        fused = insert_gradient_exchange(_medium_program(MEDIUM_BATCH // world), count)
+        sources[f"medium_fused_n{world}"] = codegen.generate(fused, inplace_outputs={1 + count + i: i for i in range(count)}, world=world).source
     return sources
 
 
@@ -234,6 +239,9 @@ def main() -> None:
     parser.add_argument("--workload", default="c5", choices=["c5", "c5_half"],
                         help="c5_half (2048-4096-4096-4096-2048, batch 4096) is the small case used for ncu captures")
     parser.add_argument("--eager", action="store_true", help="launch the timed steps directly instead of replaying a CUDA graph")
+    parser.add_argument("--dp", default="fused", choices=["fused", "nccl"],
+                        help="N > 1: gradient exchange inside the step kernel over NVLink peer memory (fused), or "
+                             "gradient kernel -> NCCL all-reduce -> update kernel (nccl, the measured baseline)")
     args = parser.parse_args()
     global MEDIUM_SIZES, MEDIUM_BATCH
     if args.workload == "c5_half":
@@ -269,6 +277,11 @@ def main() -> None:
         kernels_per_step = 1
         status = step.runner.status
         generated = step.runner.generated
+    elif args.dp == "fused":
+        step = dp.FusedShardedTrainingStep(work.fn(), (state, x0, t0))
+        kernels_per_step = step.kernels_per_step
+        status = step.status
+        generated = step.generated
     else:
         step = dp.ShardedTrainingStep(work.fn(), (state, x0, t0))
         kernels_per_step = step.kernels_per_step
@@ -332,7 +345,7 @@ def main() -> None:
 
     # per-rank gradient-kernel duration for the roofline (CUDA events on the launching stream)
     kernel_ms = elapsed_ms / steps
-    if world > 1:
+    if world > 1 and args.dp == "nccl":
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         flat = tuple(_leaves(state)) + work.batches[0]
         stream = torch.cuda.current_stream().cuda_stream
@@ -362,7 +375,10 @@ def main() -> None:
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload} medium MLP {'-'.join(map(str, MEDIUM_SIZES))}, global batch {MEDIUM_BATCH}, BF16 compute / FP32 master, SGD lr 1e-3",
                    "global_batch": MEDIUM_BATCH, "rows_per_rank": work.batch, "resident_batches": len(work.batches),
-                   "parallelism": f"dp{world} (batch-sharded, NCCL all-reduce of the BF16 gradients)" if world > 1 else "single GPU, one kernel per step",
+                   "parallelism": (f"dp{world} (batch-sharded, BF16 gradient mean exchanged inside the step kernel over NVLink peer memory)"
+                                   if world > 1 and args.dp == "fused" else
+                                   f"dp{world} (batch-sharded, NCCL all-reduce of the BF16 gradients between two kernels)" if world > 1
+                                   else "single GPU, one kernel per step"),
                    "l2": "inputs larger than L2 (FP32 weights %d MB, %d MB per batch)" % (work.weight_elements * 4 // 2**20, work.batch * (MEDIUM_SIZES[0] + MEDIUM_SIZES[-1]) * 2 // 2**20),
                    "graph_steps": 0 if args.eager else steps},
         "latency_us": {"p50": round(statistics.median(samples), 1), "min": round(min(samples), 1), "max": round(max(samples), 1),

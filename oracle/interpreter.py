@@ -49,6 +49,23 @@ _EAGER = {
 }
 
 
+def _allreduce_mean(op: Operation, args: list) -> torch.Tensor:
+    """Mean over the ranks of the default process group (identity without one), in FP32, then rounded.
+
+    Not a reference operation: the reference has no distributed code.  It is the semantics of the
+    `allreduce` op that `passes.insert_gradient_exchange` adds for batch-sharded steps.
+    """
+    import torch.distributed as dist
+    value = args[0].float().clone()
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(value, op=dist.ReduceOp.SUM)
+        value /= dist.get_world_size()
+    return value
+
+
+_EAGER["allreduce"] = _allreduce_mean
+
+
 def run(program: Program, inputs: Sequence[torch.Tensor]) -> tuple[torch.Tensor, ...]:
     """Evaluate `program` on `inputs`; returns one tensor per program output."""
     if len(inputs) != len(program.inputs):

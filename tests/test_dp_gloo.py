@@ -86,3 +86,51 @@ def test_shard_rows_partitions_the_batch():
     assert covered == list(range(8192))
     with pytest.raises(ValueError, match="divide evenly"):
         shard_rows(10, 0, 4)
+
+
+def _exchange_rank(rank: int, port: int, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        from trainkernel_b200.passes import insert_gradient_exchange
+        work = workloads.mlp_workload("shard", SIZES, BATCH, seed=3, rows=shard_rows(BATCH, rank, WORLD))
+        n = len(work.state)
+        program, _ = tk.capture(work.fn(), (work.state, *work.batches[0]))
+        exchanged = insert_gradient_exchange(program, n)       # one program, allreduce ops inside
+        state = work.state
+        for step in range(3):
+            out = interpreter.run(exchanged, (*state, *work.batches[step % len(work.batches)]))
+            state = tuple(o.clone() for o in out[1 + n:])
+        gathered = [None] * WORLD
+        dist.all_gather_object(gathered, [p.numpy().copy() for p in state])
+        if rank == 0:
+            results.put((float(out[0]), gathered))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_program_with_allreduce_ops_matches_full_batch_oracle():
+    """`insert_gradient_exchange` + the oracle's allreduce (gloo) == the single-process full-batch step."""
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_exchange_rank, args=(rank, port, results)) for rank in range(WORLD)]
+    for p in procs:
+        p.start()
+    loss, gathered = results.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for a, b in zip(gathered[0], gathered[1]):
+        assert (a == b).all()
+    work = workloads.mlp_workload("full", SIZES, BATCH, seed=3)
+    n = len(work.state)
+    program, _ = tk.capture(work.fn(), (work.state, *work.batches[0]))
+    state = work.state
+    for step in range(3):
+        out = interpreter.run(program, (*state, *work.batches[step % len(work.batches)]))
+        state = tuple(o.clone() for o in out[1 + n:])
+    assert abs(loss - float(out[0])) <= 2e-2 * abs(float(out[0]))
+    for got, want in zip(gathered[0], state):
+        err = float((torch.from_numpy(got) - want).abs().max()) / max(float(want.abs().max()), 1e-30)
+        assert err <= 2e-2

@@ -142,3 +142,33 @@ def test_split_step_without_a_process_group_matches_oracle(exchange):
     step.status()
     assert_outputs_close((loss, grads, state), expected, 2e-2, "split step")
     assert [p.data_ptr() for p in state] == pointers
+
+
+def test_fused_exchange_step_with_one_rank_matches_oracle_and_replays():
+    """The one-kernel data-parallel form (exchange stages inside the kernel) on a single rank:
+    flags, epochs and the pull/reduce/push path all run, with this GPU as its own only peer."""
+    from trainkernel_b200 import dp, workloads
+    import trainkernel_b200 as tk
+    from oracle import interpreter
+    work = workloads.build("c2", seed=2, device="cuda")
+    cpu = workloads.build("c2", seed=2, device="cpu")
+    step = dp.FusedShardedTrainingStep(work.fn(), (work.state, *work.batches[0]))
+    assert step.generated.symmetric_bytes > 4096 and "tk::exchange_mean<" in step.generated.source
+    program, _ = tk.capture(cpu.fn(), (cpu.state, *cpu.batches[0]))
+    ref_state = tuple(cpu.state)
+    for i in range(6):                                   # several launches: the epoch advances every time
+        loss, grads, state = step(work.state, *work.batches[i % 4])
+        expected = interpreter.run(program, (*ref_state, *cpu.batches[i % 4]))
+        step.status()
+        assert_outputs_close((loss, grads, state), expected, 2e-2, f"fused step {i}")
+        ref_state = tuple(e.clone() for e in expected[5:])
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(4):
+            step(work.state, *work.batches[i % 4])
+    before = [p.clone() for p in work.state]
+    graph.replay()
+    torch.cuda.synchronize()
+    step.status()
+    assert any(not torch.equal(a, b) for a, b in zip(before, work.state))
+    assert all(bool(torch.isfinite(p).all()) for p in work.state)

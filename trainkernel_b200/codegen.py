@@ -77,6 +77,8 @@ class GeneratedKernel:
     param_bytes: int = 0
     workspace_bytes: int = 0
     cluster: int = 1                      # thread-block cluster size the kernel must be launched with
+    world: int = 1                        # ranks the kernel exchanges with (1: no exchange stages)
+    symmetric_bytes: int = 0              # size of the peer-mapped buffer the kernel expects after the program inputs
 
 
 class _Body:
@@ -122,6 +124,9 @@ class _Emitter:
             return f"reinterpret_cast<const {ctype}*>({raw})" if const else f"reinterpret_cast<{ctype}*>(const_cast<void*>({raw}))"
         if where[0] == "out":
             return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>(P.out[{where[1]}])"
+        if where[0] == "sym":
+            local = f"reinterpret_cast<uint8_t*>(const_cast<void*>(P.in[{len(self.plan.program.inputs)}]))"
+            return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>({local} + {where[1]}ULL)"
         return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>(P.ws + {where[1]}ULL)"
 
     @staticmethod
@@ -611,16 +616,28 @@ class _Emitter:
         for stage in range(plan.stages):
             if stage:
                 body.emit("tk::grid_barrier(c);")
+                if stage - 1 in plan.signal_barriers:
+                    body.emit(f"if (blockIdx.x == 0 && threadIdx.x == 0) tk::dp_signal(dp, &P.in[{len(plan.program.inputs) + 1}], {plan.world}, {stage - 1});")
                 if stage_stamps:
                     body.emit(f"if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[{stage}] = tk::global_timer_ns();")
             body.emit(f"// ---- stage {stage} ----")
             base = 0
             members = [u for u in plan.units if u.stage == stage]
             # GEMM units first: the specialised warps drain them before joining the block-wide loops
-            for unit in sorted(members, key=lambda u: (u.kind != "gemm", u.path not in ("tc", "tc2"), u.index)):
+            waited: set[int] = set()
+            for unit in sorted(members, key=lambda u: (u.kind != "gemm", u.path not in ("tc", "tc2"), u.kind == "exchange", u.index)):
+                if unit.wait_barrier is not None and unit.wait_barrier not in waited:
+                    waited.add(unit.wait_barrier)
+                    body.emit(f"tk::dp_wait(c, dp, {plan.world}, {unit.wait_barrier});   // every rank has passed grid barrier {unit.wait_barrier}")
                 body.emit("{")
                 body.depth += 1
-                if unit.kind == "gemm":
+                if unit.kind == "exchange":
+                    op = unit.root
+                    source = op.inputs[0].buffer
+                    body.emit(f"// {unit.name}: mean of {source} over {plan.world} rank(s)")
+                    body.emit(f"tk::exchange_mean<{ROUND[op.output.dtype]}, {plan.world}>(c, dp, &P.in[{len(plan.program.inputs) + 1}], "
+                              f"{plan.storage[source][1]}ULL, {plan.storage[op.output.buffer][1]}ULL, {prod(unit.dims)}LL, {base}LL, {unit.items}LL);")
+                elif unit.kind == "gemm":
                     body.emit(f"// {unit.name}: {unit.root.op} {unit.mnk} via {unit.path}")
                     self.gemm(unit, body, base)
                 elif unit.kind == "reduce":
@@ -630,7 +647,8 @@ class _Emitter:
                 body.depth -= 1
                 body.emit("}")
                 base += unit.items
-        n_in = max(1, len(plan.program.inputs))
+        exchanging = plan.symmetric_bytes > 0
+        n_in = max(1, len(plan.program.inputs) + (1 + plan.world if exchanging else 0))
         n_out = max(1, len(plan.program.outputs))
         n_maps = max(1, len(self.maps))
         n_maps_used = len(self.maps)
@@ -667,11 +685,16 @@ class _Emitter:
             entry.append("    c.epi = &epi_stage.t[0][0][0];")
         if n_maps_used:
             entry.append(f"    if (threadIdx.x < {n_maps_used}) tk::tma_prefetch_desc(&P.maps[threadIdx.x]);")
+        if exchanging:
+            entry.append("    tk::Dp dp;")
+            entry.append(f"    tk::dp_init(dp, const_cast<void*>(P.in[{len(plan.program.inputs)}]));")
         if stage_stamps:
             entry.append("    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[0] = tk::global_timer_ns();")
         tail = []
         if stage_stamps:
             tail.append(f"    __syncthreads();\n    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[{plan.stages}] = tk::global_timer_ns();")
+        if exchanging:
+            tail.append("    if (blockIdx.x == 0 && threadIdx.x == 0) tk::dp_finish(dp);")
         tail += ["    tk::ctx_finish2(c);" if plan.two_cta else f"    tk::ctx_finish(c, {use_tc});", "}", ""]
         return "\n".join(header + self.functors + entry + [body.text()] + tail)
 
@@ -700,7 +723,7 @@ def _check_broadcasts(program: Program) -> None:
 
 def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = None, fuse_pointwise: bool = True,
                  fuse_epilogues: bool = True, max_blocks: int | None = None, tensor_cores: bool = True,
-                 block_n: int | None = None, two_cta: bool | None = None) -> Plan:
+                 block_n: int | None = None, two_cta: bool | None = None, world: int = 1) -> Plan:
     """Validate, canonicalise and plan `program` (no code is emitted)."""
     validate(program)
     from .passes import canonicalize_transposed_mm
@@ -712,6 +735,8 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
         raise ValueError("trainkernel: max_blocks must be positive when provided")
     if block_n is not None and block_n not in (64, 128, 256):
         raise ValueError("trainkernel: block_n must be 64, 128 or 256")
+    if type(world) is not int or not 1 <= world <= 8:
+        raise ValueError("trainkernel: world must be between 1 and 8")
     mapping = dict(inplace_outputs or {})
     if any(type(i) is not int or type(j) is not int or not 0 <= i < len(program.outputs) or not 0 <= j < len(program.inputs)
            for i, j in mapping.items()):
@@ -726,7 +751,7 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
         if output.buffer not in produced:
             raise ValueError("trainkernel: inplace outputs must be computed values, not input views")
     return Planner(program, inplace_outputs=mapping, fuse_pointwise=fuse_pointwise, fuse_epilogues=fuse_epilogues,
-                   max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n, two_cta=two_cta).plan()
+                   max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n, two_cta=two_cta, world=world).plan()
 
 
 _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shared_skew", "split_k_gemv",
@@ -736,7 +761,8 @@ _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shar
 def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: bool = True,
              max_blocks: int | None = None, inplace_outputs: dict[int, int] | None = None,
              tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
-             two_cta: bool | None = None, raster_group: int | None = None, **reference_knobs) -> GeneratedKernel:
+             two_cta: bool | None = None, raster_group: int | None = None, world: int = 1,
+             **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -754,14 +780,15 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         raise ValueError("trainkernel: blocks_per_sm must be between 1 and 8")
     plan = plan_program(program, inplace_outputs=inplace_outputs, fuse_pointwise=fuse_pointwise,
                         fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n,
-                        two_cta=two_cta)
+                        two_cta=two_cta, world=world)
     emitter = _Emitter(plan)
     if raster_group is not None:
         if type(raster_group) is not int or not 1 <= raster_group <= 64:
             raise ValueError("trainkernel: raster_group must be between 1 and 64")
         emitter.raster_group = raster_group
     source = emitter.kernel(stage_stamps)
-    n_in, n_out = max(1, len(plan.program.inputs)), max(1, len(plan.program.outputs))
+    extra_inputs = 1 + plan.world if plan.symmetric_bytes else 0
+    n_in, n_out = max(1, len(plan.program.inputs) + extra_inputs), max(1, len(plan.program.outputs))
     n_maps = max(1, len(emitter.maps))
     param_bytes = 128 * n_maps + 8 * (n_in + n_out) + 8 * 6
     per_stage: dict[int, int] = {}
@@ -788,7 +815,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         dynamic_smem=dyn,
         grid=plan.grid,
         tensor_maps=tuple(emitter.maps),
-        input_count=len(plan.program.inputs),
+        input_count=len(plan.program.inputs) + extra_inputs,
         output_count=len(plan.program.outputs),
         stages=plan.stages,
         units=tuple((u.stage, u.kind + (":" + u.phase if u.phase else ""), u.name, u.path, u.items) for u in plan.units),
@@ -796,4 +823,6 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         param_bytes=param_bytes,
         workspace_bytes=plan.workspace_bytes,
         cluster=2 if plan.two_cta else 1,
+        world=plan.world,
+        symmetric_bytes=plan.symmetric_bytes,
     )

@@ -452,6 +452,130 @@ __device__ __forceinline__ void tile_coords(int64_t t, int tiles_m, int tiles_n,
 }
 
 // ----------------------------------------------------------------------------
+// Cross-GPU exchange over peer-mapped ("symmetric") memory, one process per GPU.
+//
+// Every rank owns one symmetric buffer of identical layout: a 4 KiB header of 32-bit words followed
+// by value regions.  Header: word 0 = number of launches completed (epoch), word 1 = this rank's
+// index, words 16 + 64 * r + k = the epoch in which rank r last passed grid barrier k.  After a grid
+// barrier that peers care about, ONE thread of the rank stores the current epoch into that word of
+// every rank's header with release semantics at system scope; everything the rank wrote before the
+// barrier (to its own or to a peer's memory) is then visible to whoever acquires the word.  Waits
+// are bounded like every other wait in this file.  Peers are only ever read with plain or relaxed
+// loads and written with plain stores: no multicast, no TMA on remote memory.
+// ----------------------------------------------------------------------------
+struct Dp {
+    uint32_t* flags;      // this rank's header
+    uint32_t epoch;       // epoch of the running launch
+    uint32_t rank;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) { uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ T ld_volatile(const void* p) {
+    T value;
+    if constexpr (sizeof(T) == 2) {
+        const unsigned short bits = *reinterpret_cast<const volatile unsigned short*>(p);
+        memcpy(&value, &bits, 2);
+    } else {
+        const uint32_t bits = *reinterpret_cast<const volatile uint32_t*>(p);
+        memcpy(&value, &bits, 4);
+    }
+    return value;
+}
+
+__device__ __forceinline__ void dp_init(Dp& d, void* symmetric_local) {
+    d.flags = reinterpret_cast<uint32_t*>(symmetric_local);
+    d.epoch = ld_relaxed_gpu(d.flags) + 1u;
+    d.rank = ld_relaxed_gpu(d.flags + 1);
+}
+// Called by one thread after grid barrier `barrier`: tell every rank that this rank passed it.
+__device__ __forceinline__ void dp_signal(const Dp& d, const void* const* peers, int world, int barrier) {
+    for (int j = 0; j < world; ++j)
+        st_release_sys(reinterpret_cast<uint32_t*>(const_cast<void*>(peers[j])) + 16 + d.rank * 64 + barrier, d.epoch);
+}
+// Called by all threads of a block: returns once every rank has passed grid barrier `barrier` of this epoch.
+__device__ __forceinline__ void dp_wait(Ctx& c, const Dp& d, int world, int barrier) {
+    if (threadIdx.x == 0 && !c.aborted()) {
+        for (int j = 0; j < world; ++j) {
+            const uint32_t* word = d.flags + 16 + j * 64 + barrier;
+            uint32_t polls = 0;
+            uint64_t start = 0;
+            while (static_cast<int32_t>(ld_acquire_sys(word) - d.epoch) < 0) {
+                if ((++polls & 0x3F) == 0) {
+                    if (start == 0) start = global_timer_ns();
+                    if (c.grid_aborted()) { *reinterpret_cast<volatile uint32_t*>(&c.sh->abort) = 1u; break; }
+                    if (global_timer_ns() - start > c.timeout_ns) { c.fail(kErrPeerFlag, static_cast<uint32_t>(j * 64 + barrier)); break; }
+                }
+            }
+            if (c.aborted()) break;
+        }
+    }
+    __syncthreads();
+}
+__device__ __forceinline__ void dp_finish(const Dp& d) { st_relaxed_gpu(d.flags, d.epoch); }
+
+// Mean over ranks of a dense value, rounded to T: chunk c (THREADS x 16 bytes) is reduced by rank
+// c % WORLD, which pulls the chunk from every rank (fixed order, FP32 sum), scales by 1/WORLD,
+// rounds, and stores the result into every rank's result region.  Every rank ends up with the
+// bit-identical mean.  `items` and `item_base` follow the unit conventions (one item = 4 owned chunks).
+template <typename R, int WORLD>
+__device__ __forceinline__ void exchange_mean(Ctx& c, const Dp& d, const void* const* peers, uint64_t src_offset,
+                                              uint64_t dst_offset, int64_t numel, int64_t item_base, int64_t items) {
+    using T = typename R::T;
+    constexpr int VEC = 16 / static_cast<int>(sizeof(T));
+    const int64_t chunk = static_cast<int64_t>(kThreads) * VEC;
+    const int64_t chunks = (numel + chunk - 1) / chunk;
+    const float scale = 1.0f / static_cast<float>(WORLD);
+    for (int64_t it = first_item(item_base); it < items && !c.aborted(); it += gridDim.x) {
+#pragma unroll 1
+        for (int u = 0; u < 4; ++u) {
+            const int64_t owned = (it * 4 + u) * WORLD + d.rank;
+            if (owned >= chunks) break;
+            const int64_t e0 = owned * chunk + static_cast<int64_t>(threadIdx.x) * VEC;
+            if (e0 >= numel) continue;
+            const uint64_t byte = static_cast<uint64_t>(e0) * sizeof(T);
+            if (e0 + VEC <= numel) {
+                uint4 raw[WORLD];
+#pragma unroll
+                for (int j = 0; j < WORLD; ++j) raw[j] = ld_relaxed_sys_v4(reinterpret_cast<const char*>(peers[j]) + src_offset + byte);
+                float sum[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) sum[e] = 0.0f;
+#pragma unroll
+                for (int j = 0; j < WORLD; ++j) {
+                    const T* part = reinterpret_cast<const T*>(&raw[j]);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) sum[e] += to_f32(part[e]);
+                }
+                uint4 packed;
+                T* out = reinterpret_cast<T*>(&packed);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) from_f32(out + e, sum[e] * scale);
+#pragma unroll
+                for (int j = 0; j < WORLD; ++j) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(const_cast<void*>(peers[j])) + dst_offset + byte) = packed;
+            } else {
+                for (int64_t e = e0; e < numel; ++e) {
+                    float sum = 0.0f;
+                    for (int j = 0; j < WORLD; ++j)
+                        sum += to_f32(ld_volatile<T>(reinterpret_cast<const char*>(peers[j]) + src_offset + e * sizeof(T)));
+                    T value;
+                    from_f32(&value, sum * scale);
+                    for (int j = 0; j < WORLD; ++j)
+                        *reinterpret_cast<T*>(reinterpret_cast<char*>(const_cast<void*>(peers[j])) + dst_offset + e * sizeof(T)) = value;
+                }
+            }
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------
 // Epilogue chunk.  tcgen05.ld hands every lane one accumulator ROW (32 consecutive columns), so a
 // warp-wide global access would touch 32 different rows.  The chunk is therefore transposed through
 // a padded shared-memory buffer: afterwards 8 (or 4) lanes share a row and each warp-wide 128-bit

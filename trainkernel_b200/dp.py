@@ -137,3 +137,90 @@ def spec_numel(shape: tuple[int, ...]) -> int:
     for extent in shape:
         total *= extent
     return total
+
+
+class _Pointer:
+    """Raw device address with the one method the launcher needs."""
+
+    def __init__(self, address: int) -> None:
+        self.address = int(address)
+
+    def data_ptr(self) -> int:
+        return self.address
+
+
+class FusedShardedTrainingStep:
+    """Batch-sharded training step as ONE kernel per rank with the gradient exchange inside it.
+
+    `passes.insert_gradient_exchange` puts an `allreduce` (mean over ranks) behind the loss and
+    behind every gradient; the planner turns each into an exchange unit that shares a stage with
+    the next backward GEMMs.  The exchanged values live in a peer-mapped buffer allocated through
+    `torch.distributed._symmetric_memory`; chunk c of a value is reduced by rank c % world, which
+    pulls the chunk from every rank over NVLink, and pushes the mean back into every rank's buffer.
+    Ranks order themselves with epoch flags stored into each other's buffer after grid barriers.
+    All ranks must launch the step the same number of times; state is updated in place and the
+    returned loss and gradients are the cross-rank means (buffers owned by this object).
+    """
+
+    def __init__(self, fn: Callable[..., Any], example_inputs: Sequence[Any], *, group: Any = None, **options: Any) -> None:
+        from .codegen import generate
+        from .passes import insert_gradient_exchange
+        if "inplace_outputs" in options or "world" in options:
+            raise ValueError("trainkernel: the sharded step derives its own state mapping and world size")
+        distributed = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if distributed else 1
+        self.rank = dist.get_rank(group) if distributed else 0
+        program, self.output_tree = capture(fn, example_inputs)
+        flat, self.input_tree = tree_flatten(tuple(example_inputs))
+        state_leaves, _ = tree_flatten(example_inputs[0])
+        n = self.count = len(state_leaves)
+        if not flat or any(t.device.type != "cuda" for t in flat):
+            raise RuntimeError("trainkernel: CUDA sm_100a GPU required; CPU IR inspection is available through capture()")
+        device = self.device = flat[0].device
+        self.program = insert_gradient_exchange(program, n)
+        verbose = options.pop("verbose", False)
+        self.generated = generate(self.program, inplace_outputs={1 + n + i: i for i in range(n)}, world=self.world, **options)
+        cubin = runtime.build_cubin(self.generated.source, verbose=verbose)
+        with torch.cuda.device(device):
+            torch.cuda.current_stream(device)
+            self.module = runtime._Module(self.generated, cubin, device)
+        # the peer-mapped buffer: header words (epoch, rank, barrier flags) then the exchanged values
+        words = self.generated.symmetric_bytes // 4
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.symmetric = symm_mem.empty(words, dtype=torch.int32, device=device)
+            self.symmetric.zero_()
+            self.symmetric[1] = self.rank
+            torch.cuda.synchronize(device)
+            handle = symm_mem.rendezvous(self.symmetric, group if group is not None else dist.group.WORLD)
+            self._handle = handle
+            peers = [int(p) for p in handle.buffer_ptrs]
+            dist.barrier(group)
+        else:
+            self.symmetric = torch.zeros(words, dtype=torch.int32, device=device)
+            peers = [self.symmetric.data_ptr()]
+        self._extra = [_Pointer(self.symmetric.data_ptr())] + [_Pointer(p) for p in peers]
+        self._checker = runtime.CompiledProgram(program, self.generated, self.module, device, {1 + n + i: i for i in range(n)})
+        self.loss = torch.zeros((), dtype=torch.float32, device=device)
+        self.gradients = tuple(torch.empty(spec.shape, dtype=getattr(torch, spec.dtype), device=device)
+                               for spec in program.outputs[1:1 + n])
+        self.workspace = torch.empty(self.generated.workspace_elements, dtype=torch.float32, device=device)
+
+    @property
+    def kernels_per_step(self) -> int:
+        return 1
+
+    def __call__(self, *args: Any):
+        flat, tree = tree_flatten(args)
+        if tree != self.input_tree:
+            raise ValueError("trainkernel: runtime input pytree differs from the compiled signature")
+        flat = tuple(flat)
+        self._checker._validate_inputs(flat)
+        state = flat[:self.count]
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self.module.launch((*flat, *self._extra), (self.loss, *self.gradients, *state), self.workspace, stream)
+        torch.autograd.graph.increment_version(list(state))
+        return tree_unflatten([self.loss, *self.gradients, *state], self.output_tree)
+
+    def status(self) -> None:
+        self._checker.status()

@@ -203,3 +203,47 @@ def _split_narrow(program: Program, n: int) -> tuple[Program, Program]:
     gradient_half = Program(program.inputs, tuple(first), (program.outputs[0], *cuts))
     update_half = Program(tuple(state_inputs) + tuple(cuts), tuple(later), tuple(program.outputs[1:]))
     return gradient_half, update_half
+
+
+def insert_gradient_exchange(program: Program, state_count: int) -> Program:
+    """Rewrite a training program so that its loss and gradients are averaged across ranks in place.
+
+    After the value each gradient is derived from (the 16-bit value under the FP32 widening cast
+    when there is one, else the gradient itself) an `allreduce` operation is inserted, and every
+    later reader is pointed at its result.  `allreduce` means "element-wise mean over all ranks of
+    the job, rounded to the value's dtype"; with one rank it is the identity.  The rewritten
+    program still follows the `(loss, grads..., updated...)` contract, so it compiles to ONE kernel
+    whose exchange stages sit between the backward GEMMs and the updates that consume them.
+    """
+    n = state_count
+    if len(program.outputs) != 1 + 2 * n:
+        raise ValueError("trainkernel: exchange requires (loss, gradients, updated state) outputs")
+    producer = {op.output.buffer: op for op in program.operations}
+    cuts: list[str] = []
+    for spec in program.outputs[:1 + n]:
+        op = producer.get(spec.buffer)
+        if op is None:
+            raise ValueError("trainkernel: loss and gradients must be computed values to be exchanged")
+        source = op.inputs[0] if op.op == "cast" and op.inputs else None
+        if (isinstance(source, TensorSpec) and source.buffer in producer and source.dtype in ("bfloat16", "float16")
+                and spec.dtype == "float32"):
+            cuts.append(source.buffer)
+        else:
+            cuts.append(spec.buffer)
+    if len(set(cuts)) != len(cuts):
+        raise ValueError("trainkernel: loss and gradient values must be distinct")
+    renamed = {buffer: buffer + "_avg" for buffer in cuts}
+
+    def redirect(value):
+        if isinstance(value, TensorSpec) and value.buffer in renamed:
+            return replace(value, buffer=renamed[value.buffer])
+        return value
+
+    operations: list[Operation] = []
+    for op in program.operations:
+        operations.append(replace(op, inputs=tuple(redirect(v) for v in op.inputs)))
+        if op.output.buffer in renamed:
+            name = renamed[op.output.buffer]
+            result = TensorSpec(name, op.output.shape, op.output.dtype, row_major(op.output.shape), name)
+            operations.append(Operation(name, "allreduce", (op.output,), result, {}))
+    return Program(program.inputs, tuple(operations), tuple(redirect(v) for v in program.outputs))

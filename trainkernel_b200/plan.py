@@ -26,6 +26,8 @@ from .ir import Operation, Program, TensorSpec, row_major
 POINTWISE = frozenset({"add", "sub", "mul", "div", "neg", "relu", "pow", "threshold_backward", "full", "cast"})
 REDUCE = frozenset({"sum", "mean"})
 GEMM = frozenset({"mm", "addmm"})
+EXCHANGE = frozenset({"allreduce"})
+SYM_HEADER = 4096                      # flag words at the start of the symmetric buffer
 ELEMENT_BYTES = {"float32": 4, "float16": 2, "bfloat16": 2}
 SM_COUNT = 148
 THREADS = 192
@@ -85,7 +87,7 @@ class GemmOperand:
 
 @dataclass
 class Unit:
-    kind: str                              # "gemm" | "reduce" | "point"
+    kind: str                              # "gemm" | "reduce" | "point" | "exchange"
     name: str
     index: int                             # program position of the root / seed (ordering key)
     dims: tuple[int, ...]                  # element index space of the DAG
@@ -112,6 +114,7 @@ class Unit:
     phase: str = ""                        # "" | "partial" | "finish"
     scratch: str = ""                      # partial-sum buffer name
     vector: bool = False                   # thread strategy: 8 adjacent outputs per thread
+    wait_barrier: int | None = None        # peers must have passed this grid barrier before the unit starts
     items: int = 1
 
     @property
@@ -163,12 +166,15 @@ class Plan:
     tensor_core_units: int
     uses_tc: bool
     two_cta: bool = False
+    world: int = 1
+    symmetric_bytes: int = 0
+    signal_barriers: tuple = ()            # grid barriers after which this rank raises its flag at every peer
 
 
 class Planner:
     def __init__(self, program: Program, *, inplace_outputs: dict[int, int] | None = None,
                  fuse_pointwise: bool = True, fuse_epilogues: bool = True, max_blocks: int | None = None,
-                 tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None):
+                 tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None, world: int = 1):
         self.program = program
         self.inplace = dict(inplace_outputs or {})
         self.fuse_pointwise = fuse_pointwise
@@ -177,6 +183,7 @@ class Planner:
         self.tensor_cores = tensor_cores
         self.forced_block_n = block_n
         self.two_cta = two_cta
+        self.world = world
         self.ops = list(program.operations)
         self.index = {op.output.buffer: i for i, op in enumerate(self.ops)}
         self.producer = {op.output.buffer: op for op in self.ops}
@@ -451,6 +458,9 @@ class Planner:
                 unit = self._make_gemm(position, op)
             elif op.op in REDUCE:
                 unit = self._make_reduce(position, op)
+            elif op.op in EXCHANGE:
+                unit = Unit("exchange", op.name, position, (max(1, prod(op.output.shape)),), root=op)
+                unit.pmaps[op.output.buffer] = self._member_pmap(unit, op.output.shape) or tuple([None] * len(op.output.shape))
             elif op.op in POINTWISE:
                 continue
             else:
@@ -459,7 +469,8 @@ class Planner:
             units.append(unit)
         if self.fuse_epilogues:
             for unit in units:
-                self._grow(unit, unit.index)
+                if unit.kind != "exchange":
+                    self._grow(unit, unit.index)
         # remaining pointwise operations: inline or seed pointwise units
         for position, op in enumerate(self.ops):
             buffer = op.output.buffer
@@ -484,6 +495,12 @@ class Planner:
                 self._finish_gemm(unit)
             elif unit.kind == "reduce":
                 self._finish_reduce(unit)
+            elif unit.kind == "exchange":
+                source = unit.root.inputs[0]
+                if not isinstance(source, TensorSpec) or not _dense(source) or source.shape != unit.root.output.shape \
+                        or source.buffer in self.input_index or self._inlinable(source.buffer):
+                    raise ValueError("trainkernel: allreduce needs a dense computed value")
+                unit.source = Load(Access(source.buffer, source.dtype, 0, (1,)))
             for member in unit.members:
                 unit.exprs[member.output.buffer] = self._apply(unit, member, unit.pmaps[member.output.buffer], unit.index)
 
@@ -528,6 +545,18 @@ class Planner:
 
         # output binding
         storage: dict[str, tuple] = {spec.buffer: ("in", i) for i, spec in enumerate(program.inputs)}
+        # values that cross ranks live in the symmetric buffer: this rank's contribution and the reduced result
+        symmetric = SYM_HEADER
+        for unit in units:
+            if unit.kind != "exchange":
+                continue
+            source = unit.root.inputs[0].buffer
+            size = -(-max(1, prod(shapes[source])) * ELEMENT_BYTES[dtypes[source]] // ALIGN) * ALIGN
+            for buffer in (source, unit.root.output.buffer):
+                if buffer in storage:
+                    raise ValueError("trainkernel: an exchanged value cannot also be an input or an exchange result")
+                storage[buffer] = ("sym", symmetric)
+                symmetric += size
         native: dict[int, str] = {}
         copies: list[tuple[int, TensorSpec]] = []
         direct_candidates: dict[int, int] = {}
@@ -610,6 +639,16 @@ class Planner:
         if not self._assign_stages(units, writer, ordering):
             raise ValueError("trainkernel: cyclic stage constraints")
 
+        # cross-rank ordering: pulls and reads of pushed results wait for the peers' previous barrier
+        remote = {u.root.output.buffer for u in units if u.kind == "exchange"}
+        signal: set[int] = set()
+        for unit in units:
+            if unit.kind == "exchange" or unit.reads & remote:
+                if unit.stage == 0:
+                    raise ValueError("trainkernel: an exchange cannot be scheduled in the first stage")
+                unit.wait_barrier = unit.stage - 1
+                signal.add(unit.stage - 1)
+
         # workspace arena
         stage_count = max((u.stage for u in units), default=0) + 1
         last_read: dict[str, int] = {}
@@ -663,7 +702,8 @@ class Planner:
         if two_cta:
             grid = max(2, grid - grid % 2)
         return Plan(program, sorted(units, key=lambda u: (u.stage, u.index)), stage_count, storage, dtypes, shapes,
-                    max(total, ALIGN), inlined, direct, staged, native, grid, tc_units, tc_units > 0, two_cta)
+                    max(total, ALIGN), inlined, direct, staged, native, grid, tc_units, tc_units > 0, two_cta,
+                    self.world, symmetric if symmetric > SYM_HEADER else 0, tuple(sorted(signal)))
 
     # -- helpers ---------------------------------------------------------------------
     def _refs(self, expr) -> set[str]:
@@ -809,6 +849,11 @@ class Planner:
                 unit.items = -(-n // per)
             else:
                 unit.items = -(-m // 32) * -(-n // 32)
+        elif unit.kind == "exchange":
+            # one item = 4 owned chunks of THREADS x 16 bytes; chunk c belongs to rank c % world
+            nbytes = prod(unit.dims) * ELEMENT_BYTES[unit.root.output.dtype]
+            chunks = -(-nbytes // (THREADS * 16))
+            unit.items = max(1, -(-(-(-chunks // self.world)) // 4))
         elif unit.kind == "reduce":
             outputs = prod(unit.kept)
             if unit.phase == "finish":
