@@ -148,3 +148,27 @@ def test_medium_mlp_plan_fits_and_uses_wide_tiles():
     single = generate(program, inplace_outputs={9 + i: i for i in range(8)}, two_cta=False)
     assert single.cluster == 1 and "tk::gemm_tc<256" in single.source
     assert len(g.tensor_maps) == 22 and g.param_bytes <= 4096
+
+
+def test_exchange_units_overlap_backward_gemms_and_precede_updates():
+    from trainkernel_b200.passes import insert_gradient_exchange
+    program, inplace = _step_program("c2")
+    exchanged = insert_gradient_exchange(program, 4)
+    assert sum(op.op == "allreduce" for op in exchanged.operations) == 5          # loss + 4 gradients
+    plan = plan_program(exchanged, inplace_outputs=inplace, world=2)
+    by_name = {u.name: u for u in plan.units}
+    assert by_name["mm_2_avg"].kind == "exchange"
+    # dW2 is averaged in the stage that computes dW1; the SGD update that consumes the mean follows
+    assert by_name["mm_2_avg"].stage == by_name["mm_2"].stage + 1 == by_name["mm_4"].stage
+    consumer = next(u for u in plan.units if "mm_2_avg" in u.reads)
+    assert consumer.stage == by_name["mm_2_avg"].stage + 1 and consumer.wait_barrier == consumer.stage - 1
+    assert by_name["mm_2_avg"].wait_barrier == by_name["mm_2_avg"].stage - 1
+    assert set(plan.signal_barriers) == {u.wait_barrier for u in plan.units if u.wait_barrier is not None}
+    assert plan.storage["mm_2"][0] == "sym" and plan.storage["mm_2_avg"][0] == "sym" and plan.symmetric_bytes > 4096
+    assert len(plan.direct_commits) == 4                                           # updates still commit in place
+    g = generate(exchanged, inplace_outputs=inplace, world=2)
+    assert g.input_count == len(program.inputs) + 1 + 2 and g.world == 2
+    assert "tk::exchange_mean<tk::BF16, 2>" in g.source and "tk::dp_signal" in g.source and "tk::dp_wait" in g.source
+    assert runtime.build_cubin(g.source)[:4] == b"\x7fELF"
+    with pytest.raises(ValueError, match="world"):
+        generate(exchanged, inplace_outputs=inplace, world=9)

@@ -524,7 +524,9 @@ __device__ __forceinline__ void dp_finish(const Dp& d) { st_relaxed_gpu(d.flags,
 // Mean over ranks of a dense value, rounded to T: chunk c (THREADS x 16 bytes) is reduced by rank
 // c % WORLD, which pulls the chunk from every rank (fixed order, FP32 sum), scales by 1/WORLD,
 // rounds, and stores the result into every rank's result region.  Every rank ends up with the
-// bit-identical mean.  `items` and `item_base` follow the unit conventions (one item = 4 owned chunks).
+// bit-identical mean.  `items` and `item_base` follow the unit conventions (one item = 8 owned chunks).
+constexpr int kExchangeChunksPerItem = 8;
+
 template <typename R, int WORLD>
 __device__ __forceinline__ void exchange_mean(Ctx& c, const Dp& d, const void* const* peers, uint64_t src_offset,
                                               uint64_t dst_offset, int64_t numel, int64_t item_base, int64_t items) {
@@ -533,42 +535,54 @@ __device__ __forceinline__ void exchange_mean(Ctx& c, const Dp& d, const void* c
     const int64_t chunk = static_cast<int64_t>(kThreads) * VEC;
     const int64_t chunks = (numel + chunk - 1) / chunk;
     const float scale = 1.0f / static_cast<float>(WORLD);
+    // G chunks are pulled together so that G * WORLD 128-bit loads per thread are in flight: a remote
+    // load takes a few microseconds, and NVLink only fills up with megabytes outstanding per GPU.
+    constexpr int G = WORLD <= 2 ? 8 : (WORLD <= 4 ? 4 : 2);
     for (int64_t it = first_item(item_base); it < items && !c.aborted(); it += gridDim.x) {
 #pragma unroll 1
-        for (int u = 0; u < 4; ++u) {
-            const int64_t owned = (it * 4 + u) * WORLD + d.rank;
-            if (owned >= chunks) break;
-            const int64_t e0 = owned * chunk + static_cast<int64_t>(threadIdx.x) * VEC;
-            if (e0 >= numel) continue;
-            const uint64_t byte = static_cast<uint64_t>(e0) * sizeof(T);
-            if (e0 + VEC <= numel) {
-                uint4 raw[WORLD];
+        for (int u0 = 0; u0 < kExchangeChunksPerItem; u0 += G) {
+            uint4 raw[G][WORLD];
+            int64_t e0[G];
 #pragma unroll
-                for (int j = 0; j < WORLD; ++j) raw[j] = ld_relaxed_sys_v4(reinterpret_cast<const char*>(peers[j]) + src_offset + byte);
-                float sum[VEC];
+            for (int g = 0; g < G; ++g) {
+                const int64_t owned = (it * kExchangeChunksPerItem + u0 + g) * WORLD + d.rank;
+                e0[g] = owned < chunks ? owned * chunk + static_cast<int64_t>(threadIdx.x) * VEC : numel;
+                if (e0[g] + VEC <= numel) {
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) sum[e] = 0.0f;
-#pragma unroll
-                for (int j = 0; j < WORLD; ++j) {
-                    const T* part = reinterpret_cast<const T*>(&raw[j]);
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) sum[e] += to_f32(part[e]);
+                    for (int j = 0; j < WORLD; ++j)
+                        raw[g][j] = ld_relaxed_sys_v4(reinterpret_cast<const char*>(peers[j]) + src_offset + static_cast<uint64_t>(e0[g]) * sizeof(T));
                 }
-                uint4 packed;
-                T* out = reinterpret_cast<T*>(&packed);
+            }
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) from_f32(out + e, sum[e] * scale);
+            for (int g = 0; g < G; ++g) {
+                if (e0[g] >= numel) continue;
+                const uint64_t byte = static_cast<uint64_t>(e0[g]) * sizeof(T);
+                if (e0[g] + VEC <= numel) {
+                    float sum[VEC];
 #pragma unroll
-                for (int j = 0; j < WORLD; ++j) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(const_cast<void*>(peers[j])) + dst_offset + byte) = packed;
-            } else {
-                for (int64_t e = e0; e < numel; ++e) {
-                    float sum = 0.0f;
-                    for (int j = 0; j < WORLD; ++j)
-                        sum += to_f32(ld_volatile<T>(reinterpret_cast<const char*>(peers[j]) + src_offset + e * sizeof(T)));
-                    T value;
-                    from_f32(&value, sum * scale);
-                    for (int j = 0; j < WORLD; ++j)
-                        *reinterpret_cast<T*>(reinterpret_cast<char*>(const_cast<void*>(peers[j])) + dst_offset + e * sizeof(T)) = value;
+                    for (int e = 0; e < VEC; ++e) sum[e] = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < WORLD; ++j) {
+                        const T* part = reinterpret_cast<const T*>(&raw[g][j]);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) sum[e] += to_f32(part[e]);
+                    }
+                    uint4 packed;
+                    T* out = reinterpret_cast<T*>(&packed);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) from_f32(out + e, sum[e] * scale);
+#pragma unroll
+                    for (int j = 0; j < WORLD; ++j) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(const_cast<void*>(peers[j])) + dst_offset + byte) = packed;
+                } else {
+                    for (int64_t e = e0[g]; e < numel; ++e) {
+                        float sum = 0.0f;
+                        for (int j = 0; j < WORLD; ++j)
+                            sum += to_f32(ld_volatile<T>(reinterpret_cast<const char*>(peers[j]) + src_offset + e * sizeof(T)));
+                        T value;
+                        from_f32(&value, sum * scale);
+                        for (int j = 0; j < WORLD; ++j)
+                            *reinterpret_cast<T*>(reinterpret_cast<char*>(const_cast<void*>(peers[j])) + dst_offset + e * sizeof(T)) = value;
+                    }
                 }
             }
         }

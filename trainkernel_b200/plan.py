@@ -850,10 +850,10 @@ class Planner:
             else:
                 unit.items = -(-m // 32) * -(-n // 32)
         elif unit.kind == "exchange":
-            # one item = 4 owned chunks of THREADS x 16 bytes; chunk c belongs to rank c % world
+            # one item = 8 owned chunks of THREADS x 16 bytes; chunk c belongs to rank c % world
             nbytes = prod(unit.dims) * ELEMENT_BYTES[unit.root.output.dtype]
             chunks = -(-nbytes // (THREADS * 16))
-            unit.items = max(1, -(-(-(-chunks // self.world)) // 4))
+            unit.items = max(1, -(-(-(-chunks // self.world)) // 8))
         elif unit.kind == "reduce":
             outputs = prod(unit.kept)
             if unit.phase == "finish":
