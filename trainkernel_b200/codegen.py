@@ -114,6 +114,7 @@ class _Emitter:
         self.needs_simt = False
         self.raster_group = 8
         self.rows = False
+        self.background = True
 
     # -- addressing ------------------------------------------------------------------
     def pointer(self, buffer: str, dtype: str, const: bool) -> str:
@@ -339,7 +340,7 @@ class _Emitter:
         self.maps.append(spec)
         return len(self.maps) - 1, not k_major
 
-    def gemm(self, unit: Unit, body: _Body, base: int) -> None:
+    def gemm(self, unit: Unit, body: _Body, base: int, bg: str = "tk::NoBg") -> None:
         epi = self.functor(unit)
         m, n, k = unit.mnk
         a, b = unit.a, unit.b
@@ -348,7 +349,7 @@ class _Emitter:
             flipped = type(b)(b.buffer, b.dtype, b.round_to, b.offset, (b.strides[1], b.strides[0]))
             ib, b_mn = self._tensor_map(flipped, n, k, 128)
             fmt = 1 if a.dtype == "bfloat16" else 0
-            body.emit(f"tk::gemm_tc2<{str(a_mn).lower()}, {str(b_mn).lower()}, {fmt}, {self.raster_group}, {epi}>"
+            body.emit(f"tk::gemm_tc2<{str(a_mn).lower()}, {str(b_mn).lower()}, {fmt}, {self.raster_group}, {epi}, {bg}>"
                       f"(c, P, &P.maps[{ia}], &P.maps[{ib}], {m}, {n}, {k}, {base}LL);")
         elif unit.path == "tc":
             ia, a_mn = self._tensor_map(a, m, k, 128)
@@ -356,7 +357,7 @@ class _Emitter:
             flipped = type(b)(b.buffer, b.dtype, b.round_to, b.offset, (b.strides[1], b.strides[0]))
             ib, b_mn = self._tensor_map(flipped, n, k, unit.block_n)
             fmt = 1 if a.dtype == "bfloat16" else 0
-            body.emit(f"tk::gemm_tc<{unit.block_n}, {str(a_mn).lower()}, {str(b_mn).lower()}, {fmt}, {epi}>"
+            body.emit(f"tk::gemm_tc<{unit.block_n}, {str(a_mn).lower()}, {str(b_mn).lower()}, {fmt}, {epi}, {bg}>"
                       f"(c, P, &P.maps[{ia}], &P.maps[{ib}], {m}, {n}, {k}, {base}LL);")
         elif unit.path == "gemv":
             k_major = b.strides[0] == 1 and b.strides[1] != 1
@@ -401,49 +402,54 @@ class _Emitter:
             walk(expr)
         return all(all(a.strides[d] == dense[d] for d in live) or not any(a.strides[d] for d in live) for a in found)
 
+    def point_item(self, unit: Unit, body: _Body, tid: str) -> None:
+        """Body of one item `it` of a flat pointwise unit for the thread slot `tid` (0..THREADS-1)."""
+        total = prod(unit.dims)
+        # collapse to one dimension, 8 consecutive elements per thread
+        flat = Unit(unit.kind, unit.name, unit.index, (total,))
+        flat.members, flat.stores = unit.members, unit.stores
+        dense = row_major(unit.dims)
+        live = [d for d, n in enumerate(unit.dims) if n > 1]
+
+        def rebase(expr):
+            if isinstance(expr, Load):
+                a = expr.access
+                unit_stride = 1 if live and all(a.strides[d] == dense[d] for d in live) else 0
+                if not live:
+                    unit_stride = 0
+                return Load(Access(a.buffer, a.dtype, a.offset, (unit_stride,)))
+            if isinstance(expr, Apply):
+                return Apply(expr.op, tuple(rebase(arg) for arg in expr.args))
+            return expr
+
+        flat.exprs = {k: rebase(v) for k, v in unit.exprs.items()}
+        unroll = point_unroll(total, len(unit.reads) + len(unit.stores))
+        # Each thread owns `unroll` chunks of 8 consecutive elements, THREADS * 8 elements apart, so every
+        # 128-bit access of a warp is contiguous; all loads are issued before the first store.
+        envs = []
+        for u in range(unroll):
+            body.emit(f"const int64_t i{u} = (it * {unroll}LL + {u}LL) * {THREADS * 8}LL + ({tid}) * 8;")
+            body.emit(f"const int n{u} = (int)tk::imin(8, tk::imax(0, {total}LL - i{u}));")
+            env: dict = {}
+            for expr in flat.exprs.values():
+                self._preload(expr, body, env, "8", [f"i{u}"], f"n{u}")
+            envs.append(env)
+        for u in range(unroll):
+            body.emit(f"if (n{u} > 0) {{")
+            body.depth += 1
+            self.dag(flat, body, envs[u], "8", [f"i{u}"], f"n{u}")
+            body.depth -= 1
+            body.emit("}")
+
     def point(self, unit: Unit, body: _Body, base: int) -> None:
         total = prod(unit.dims)
         if total == 0:
             return
         body.emit(f"// {unit.name}: pointwise over {list(unit.dims)}")
         if self._flat_ok(unit):
-            # collapse to one dimension, 8 consecutive elements per thread
-            flat = Unit(unit.kind, unit.name, unit.index, (total,))
-            flat.members, flat.stores = unit.members, unit.stores
-            dense = row_major(unit.dims)
-            live = [d for d, n in enumerate(unit.dims) if n > 1]
-
-            def rebase(expr):
-                if isinstance(expr, Load):
-                    a = expr.access
-                    unit_stride = 1 if live and all(a.strides[d] == dense[d] for d in live) else 0
-                    if not live:
-                        unit_stride = 0
-                    return Load(Access(a.buffer, a.dtype, a.offset, (unit_stride,)))
-                if isinstance(expr, Apply):
-                    return Apply(expr.op, tuple(rebase(arg) for arg in expr.args))
-                return expr
-
-            flat.exprs = {k: rebase(v) for k, v in unit.exprs.items()}
-            unroll = point_unroll(total)
             body.emit(f"for (int64_t it = tk::first_item({base}LL); it < {unit.items}LL; it += gridDim.x) {{")
             body.depth += 1
-            # Each thread owns `unroll` chunks of 8 consecutive elements, {THREADS * 8} elements apart, so every
-            # 128-bit access of a warp is contiguous; all loads are issued before the first store.
-            envs = []
-            for u in range(unroll):
-                body.emit(f"const int64_t i{u} = (it * {unroll}LL + {u}LL) * {THREADS * 8}LL + threadIdx.x * 8;")
-                body.emit(f"const int n{u} = (int)tk::imin(8, tk::imax(0, {total}LL - i{u}));")
-                env: dict = {}
-                for expr in flat.exprs.values():
-                    self._preload(expr, body, env, "8", [f"i{u}"], f"n{u}")
-                envs.append(env)
-            for u in range(unroll):
-                body.emit(f"if (n{u} > 0) {{")
-                body.depth += 1
-                self.dag(flat, body, envs[u], "8", [f"i{u}"], f"n{u}")
-                body.depth -= 1
-                body.emit("}")
+            self.point_item(unit, body, "threadIdx.x")
             body.depth -= 1
             body.emit("}")
             return
@@ -617,36 +623,79 @@ class _Emitter:
             if stage:
                 body.emit("tk::grid_barrier(c);")
                 if stage - 1 in plan.signal_barriers:
-                    body.emit(f"if (blockIdx.x == 0 && threadIdx.x == 0) tk::dp_signal(dp, &P.in[{len(plan.program.inputs) + 1}], {plan.world}, {stage - 1});")
+                    body.emit(f"if (blockIdx.x == 0 && threadIdx.x == 0) tk::dp_signal(c.dp, &P.in[{len(plan.program.inputs) + 1}], {plan.world}, {stage - 1});")
                 if stage_stamps:
                     body.emit(f"if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[{stage}] = tk::global_timer_ns();")
             body.emit(f"// ---- stage {stage} ----")
             base = 0
             members = [u for u in plan.units if u.stage == stage]
-            # GEMM units first: the specialised warps drain them before joining the block-wide loops
-            waited: set[int] = set()
-            for unit in sorted(members, key=lambda u: (u.kind != "gemm", u.path not in ("tc", "tc2"), u.kind == "exchange", u.index)):
-                if unit.wait_barrier is not None and unit.wait_barrier not in waited:
-                    waited.add(unit.wait_barrier)
-                    body.emit(f"tk::dp_wait(c, dp, {plan.world}, {unit.wait_barrier});   // every rank has passed grid barrier {unit.wait_barrier}")
+            ordered = sorted(members, key=lambda u: (u.kind != "gemm", u.path not in ("tc", "tc2"), u.kind == "exchange", u.index))
+            bases = {}
+            for unit in ordered:
+                bases[id(unit)] = base
+                base += unit.items
+            peers = f"&P.in[{len(plan.program.inputs) + 1}]"
+            # cross-rank ordering first: background work may start as soon as the stage does
+            for barrier in sorted({u.wait_barrier for u in members if u.wait_barrier is not None}):
+                body.emit(f"tk::dp_wait(c, c.dp, {plan.world}, {barrier});   // every rank has passed grid barrier {barrier}")
+            # memory-bound units that the epilogue warps run while they wait for the tensor pipe
+            tensor_units = [u for u in ordered if u.kind == "gemm" and u.path in ("tc", "tc2")]
+            background = [u for u in ordered if tensor_units and self.background and
+                          (u.kind == "exchange" or (u.kind == "point" and prod(u.dims) and self._flat_ok(u)))]
+            bg = "tk::NoBg"
+            if background:
+                bg = f"Bg_{stage}"
+                runs, totals = [], []
+                for k, unit in enumerate(background):
+                    fn = _Body()
+                    fn.depth = 1
+                    if unit.kind == "exchange":
+                        op = unit.root
+                        source = op.inputs[0].buffer
+                        fn.emit(f"tk::exchange_mean_item<{ROUND[op.output.dtype]}, {plan.world}>(c.dp, {peers}, {plan.storage[source][1]}ULL, "
+                                f"{plan.storage[op.output.buffer][1]}ULL, {prod(unit.dims)}LL, it, tid);")
+                    else:
+                        self.point_item(unit, fn, "tid")
+                    self.functors.append(f"// {unit.name} ({unit.kind}) of stage {stage}, one 32-thread slice of item `it`\n"
+                                         f"static __device__ __noinline__ void bg_{stage}_{k}(const Params& P, tk::Ctx& c, int64_t it, int tid) {{\n{fn.text()}\n}}\n")
+                    b, n = bases[id(unit)], unit.items
+                    totals.append(f"tk::owned_items({b}LL, {n}LL)")
+                    runs.append(f"        {{ const int64_t n = tk::owned_items({b}LL, {n}LL) * {THREADS // 32}; if (o < n) {{ bg_{stage}_{k}(P, c, tk::first_item({b}LL) + (o / {THREADS // 32}) * gridDim.x, "
+                                f"(int)(o % {THREADS // 32}) * 32 + lane); return; }} o -= n; }}")
+                self.functors.append(
+                    f"struct Bg_{stage} {{\n    static constexpr bool kActive = true;\n"
+                    f"    static __device__ __forceinline__ int total() {{ return (int)({THREADS // 32} * ({' + '.join(totals)})); }}\n"
+                    f"    static __device__ __forceinline__ void run(const Params& P, tk::Ctx& c, int ordinal, int lane) {{\n        int64_t o = ordinal;\n"
+                    + "\n".join(runs) + "\n    }\n};\n")
+                body.emit(f"if (threadIdx.x == 0) {{ shared_state.bg_next = 0; shared_state.bg_total = {bg}::total(); }}")
+                body.emit("__syncthreads();")
+            for unit in ordered:
+                if unit in background:
+                    continue
+                if background and unit.kind != "gemm" or (background and unit.kind == "gemm" and unit.path not in ("tc", "tc2")):
+                    if not getattr(self, "_drained", None) == stage:
+                        self._drained = stage
+                        body.emit(f"tk::bg_drain<{bg}>(c, P);   // whatever background work is left, by all warps")
                 body.emit("{")
                 body.depth += 1
                 if unit.kind == "exchange":
                     op = unit.root
                     source = op.inputs[0].buffer
                     body.emit(f"// {unit.name}: mean of {source} over {plan.world} rank(s)")
-                    body.emit(f"tk::exchange_mean<{ROUND[op.output.dtype]}, {plan.world}>(c, dp, &P.in[{len(plan.program.inputs) + 1}], "
-                              f"{plan.storage[source][1]}ULL, {plan.storage[op.output.buffer][1]}ULL, {prod(unit.dims)}LL, {base}LL, {unit.items}LL);")
+                    body.emit(f"tk::exchange_mean<{ROUND[op.output.dtype]}, {plan.world}>(c, {peers}, "
+                              f"{plan.storage[source][1]}ULL, {plan.storage[op.output.buffer][1]}ULL, {prod(unit.dims)}LL, {bases[id(unit)]}LL, {unit.items}LL);")
                 elif unit.kind == "gemm":
                     body.emit(f"// {unit.name}: {unit.root.op} {unit.mnk} via {unit.path}")
-                    self.gemm(unit, body, base)
+                    self.gemm(unit, body, bases[id(unit)], bg if unit.path in ("tc", "tc2") else "tk::NoBg")
                 elif unit.kind == "reduce":
-                    self.reduce(unit, body, base)
+                    self.reduce(unit, body, bases[id(unit)])
                 else:
-                    self.point(unit, body, base)
+                    self.point(unit, body, bases[id(unit)])
                 body.depth -= 1
                 body.emit("}")
-                base += unit.items
+            if background and getattr(self, "_drained", None) != stage:
+                self._drained = stage
+                body.emit(f"tk::bg_drain<{bg}>(c, P);   // whatever background work is left, by all warps")
         exchanging = plan.symmetric_bytes > 0
         n_in = max(1, len(plan.program.inputs) + (1 + plan.world if exchanging else 0))
         n_out = max(1, len(plan.program.outputs))
@@ -686,15 +735,14 @@ class _Emitter:
         if n_maps_used:
             entry.append(f"    if (threadIdx.x < {n_maps_used}) tk::tma_prefetch_desc(&P.maps[threadIdx.x]);")
         if exchanging:
-            entry.append("    tk::Dp dp;")
-            entry.append(f"    tk::dp_init(dp, const_cast<void*>(P.in[{len(plan.program.inputs)}]));")
+            entry.append(f"    tk::dp_init(c.dp, const_cast<void*>(P.in[{len(plan.program.inputs)}]));")
         if stage_stamps:
             entry.append("    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[0] = tk::global_timer_ns();")
         tail = []
         if stage_stamps:
             tail.append(f"    __syncthreads();\n    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[{plan.stages}] = tk::global_timer_ns();")
         if exchanging:
-            tail.append("    if (blockIdx.x == 0 && threadIdx.x == 0) tk::dp_finish(dp);")
+            tail.append("    if (blockIdx.x == 0 && threadIdx.x == 0) tk::dp_finish(c.dp);")
         tail += ["    tk::ctx_finish2(c);" if plan.two_cta else f"    tk::ctx_finish(c, {use_tc});", "}", ""]
         return "\n".join(header + self.functors + entry + [body.text()] + tail)
 

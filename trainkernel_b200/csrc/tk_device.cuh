@@ -124,10 +124,20 @@ struct SharedState {
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort;
+    int bg_next;          // next background work ordinal of this block in the current stage
+    int bg_total;         // number of background ordinals this block owns in the current stage
     float reduce[32];
 };
 
+// Cross-GPU exchange state (see the exchange section below); unused by single-GPU kernels.
+struct Dp {
+    uint32_t* flags;      // this rank's header
+    uint32_t epoch;       // epoch of the running launch
+    uint32_t rank;
+};
+
 struct Ctx {
+    Dp dp;
     uint32_t* sync;        // {count, generation} of this launch's barrier slot
     uint32_t* status;      // {code, stage, block, detail}
     uint64_t timeout_ns;
@@ -463,12 +473,6 @@ __device__ __forceinline__ void tile_coords(int64_t t, int tiles_m, int tiles_n,
 // are bounded like every other wait in this file.  Peers are only ever read with plain or relaxed
 // loads and written with plain stores: no multicast, no TMA on remote memory.
 // ----------------------------------------------------------------------------
-struct Dp {
-    uint32_t* flags;      // this rank's header
-    uint32_t epoch;       // epoch of the running launch
-    uint32_t rank;
-};
-
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) { uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory"); }
 __device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
@@ -528,8 +532,8 @@ __device__ __forceinline__ void dp_finish(const Dp& d) { st_relaxed_gpu(d.flags,
 constexpr int kExchangeChunksPerItem = 8;
 
 template <typename R, int WORLD>
-__device__ __forceinline__ void exchange_mean(Ctx& c, const Dp& d, const void* const* peers, uint64_t src_offset,
-                                              uint64_t dst_offset, int64_t numel, int64_t item_base, int64_t items) {
+__device__ __noinline__ void exchange_mean_item(const Dp& d, const void* const* peers, uint64_t src_offset,
+                                                   uint64_t dst_offset, int64_t numel, int64_t it, int tid) {
     using T = typename R::T;
     constexpr int VEC = 16 / static_cast<int>(sizeof(T));
     const int64_t chunk = static_cast<int64_t>(kThreads) * VEC;
@@ -538,7 +542,7 @@ __device__ __forceinline__ void exchange_mean(Ctx& c, const Dp& d, const void* c
     // G chunks are pulled together so that G * WORLD 128-bit loads per thread are in flight: a remote
     // load takes a few microseconds, and NVLink only fills up with megabytes outstanding per GPU.
     constexpr int G = WORLD <= 2 ? 8 : (WORLD <= 4 ? 4 : 2);
-    for (int64_t it = first_item(item_base); it < items && !c.aborted(); it += gridDim.x) {
+    {
 #pragma unroll 1
         for (int u0 = 0; u0 < kExchangeChunksPerItem; u0 += G) {
             uint4 raw[G][WORLD];
@@ -546,7 +550,7 @@ __device__ __forceinline__ void exchange_mean(Ctx& c, const Dp& d, const void* c
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 const int64_t owned = (it * kExchangeChunksPerItem + u0 + g) * WORLD + d.rank;
-                e0[g] = owned < chunks ? owned * chunk + static_cast<int64_t>(threadIdx.x) * VEC : numel;
+                e0[g] = owned < chunks ? owned * chunk + static_cast<int64_t>(tid) * VEC : numel;
                 if (e0[g] + VEC <= numel) {
 #pragma unroll
                     for (int j = 0; j < WORLD; ++j)
@@ -587,6 +591,47 @@ __device__ __forceinline__ void exchange_mean(Ctx& c, const Dp& d, const void* c
             }
         }
     }
+}
+
+template <typename R, int WORLD>
+__device__ __forceinline__ void exchange_mean(Ctx& c, const void* const* peers, uint64_t src_offset, uint64_t dst_offset,
+                                              int64_t numel, int64_t item_base, int64_t items) {
+    for (int64_t it = first_item(item_base); it < items && !c.aborted(); it += gridDim.x)
+        exchange_mean_item<R, WORLD>(c.dp, peers, src_offset, dst_offset, numel, it, threadIdx.x);
+}
+
+// ----------------------------------------------------------------------------
+// Background work.  Memory-bound units of a stage (flat pointwise streams, exchange units) are cut
+// into per-warp pieces that the epilogue warps execute while they would otherwise wait for the
+// tensor pipe, so HBM and NVLink traffic overlaps the MMAs of the same stage.  A stage's functor
+// Bg maps an ordinal of this block to (unit, item, 32-thread slice); ordinals are handed out with
+// a shared-memory counter, and whatever is left when the GEMM tiles are done is drained by all warps.
+// ----------------------------------------------------------------------------
+struct NoBg {
+    static constexpr bool kActive = false;
+    template <typename Params> static __device__ __forceinline__ void run(const Params&, Ctx&, int, int) {}
+};
+
+template <typename Bg, typename Params>
+__device__ __forceinline__ bool bg_step(Ctx& c, const Params& P) {
+    int ordinal = 0;
+    if (c.lane == 0) ordinal = atomicAdd(&c.sh->bg_next, 1);
+    ordinal = __shfl_sync(0xffffffffu, ordinal, 0);
+    if (ordinal >= *reinterpret_cast<volatile int*>(&c.sh->bg_total)) return false;
+    Bg::run(P, c, ordinal, c.lane);
+    return true;
+}
+template <typename Bg, typename Params>
+__device__ __forceinline__ void bg_drain(Ctx& c, const Params& P) {
+    if constexpr (Bg::kActive) {
+        __syncwarp();
+        while (bg_step<Bg>(c, P)) {}
+    }
+}
+// Number of items of a unit (n items starting at list position `base`) that this block owns.
+__device__ __forceinline__ int64_t owned_items(int64_t base, int64_t n) {
+    const int64_t first = first_item(base);
+    return first < n ? (n - first + gridDim.x - 1) / gridDim.x : 0;
 }
 
 // ----------------------------------------------------------------------------
@@ -639,7 +684,7 @@ __device__ __forceinline__ void epilogue_chunk(Ctx& c, const Params& P, const fl
 // {64 (MN), 64 (K)} box issued once per 64-wide MN atom.  Out-of-range parts of a box are
 // zero-filled by TMA, which is what makes M, N and K tails work.
 // ----------------------------------------------------------------------------
-template <int BN, bool A_MN, bool B_MN, int FMT, typename Epi, typename Params>
+template <int BN, bool A_MN, bool B_MN, int FMT, typename Epi, typename Bg, typename Params>
 __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorMap* map_a, const CUtensorMap* map_b,
                                         int M, int N, int K, int64_t item_base) {
     static_assert(BN % 64 == 0 && BN <= kMaxBN, "BN must be 64, 128, 192 or 256");
@@ -712,6 +757,9 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
                 int pm, pn; tile_coords(t + step, tiles_m, tiles_n, pm, pn);
                 const int prow = pm * BM + quarter * 32 + c.lane;
                 if (prow < M && pn * BN < N) Epi::prefetch(P, prow, pn * BN, min(BN, N - pn * BN));
+            }
+            if constexpr (Bg::kActive) {
+                while (!__all_sync(0xffffffffu, mbar_try(&sh->tmem_full[c.acc], c.acc_phase))) { if (!bg_step<Bg>(c, P)) break; }
             }
             if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
             tc_fence_after();

@@ -99,7 +99,7 @@ __device__ __forceinline__ void pair_coords(int64_t t, int tiles_m, int tiles_n,
 // C[M,N] = A[M,K] * B[K,N].  Tensor maps: K-major operands use a {64 (K), 128 rows} box,
 // MN-major operands a {64 (MN), 64 (K)} box per 64-wide atom (two atoms per CTA per operand).
 // `item_base` is the unit's position in the stage's item list counted in CTAs (even).
-template <bool A_MN, bool B_MN, int FMT, int GROUP, typename Epi, typename Params>
+template <bool A_MN, bool B_MN, int FMT, int GROUP, typename Epi, typename Bg, typename Params>
 __device__ __forceinline__ void gemm_tc2(Ctx& c, const Params& P, const CUtensorMap* map_a, const CUtensorMap* map_b,
                                          int M, int N, int K, int64_t item_base) {
     constexpr int TM = 256, TN = 256;
@@ -177,6 +177,9 @@ __device__ __forceinline__ void gemm_tc2(Ctx& c, const Params& P, const CUtensor
                 int pm, pn; pair_coords<GROUP>(t + clusters, tiles_m, tiles_n, pm, pn);
                 const int prow = pm * TM + static_cast<int>(rank) * 128 + quarter * 32 + c.lane;
                 if (prow < M && pn * TN < N) Epi::prefetch(P, prow, pn * TN, min(TN, N - pn * TN));
+            }
+            if constexpr (Bg::kActive) {
+                while (!__all_sync(0xffffffffu, mbar_try(&sh->tmem_full[c.acc], c.acc_phase))) { if (!bg_step<Bg>(c, P)) break; }
             }
             if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
             tc_fence_after();

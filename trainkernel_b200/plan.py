@@ -122,14 +122,14 @@ class Unit:
         return {s.buffer for s in self.stores}
 
 
-def point_unroll(total: int) -> int:
+def point_unroll(total: int, streams: int = 2) -> int:
     """Independent 8-element chunks each thread of a flat pointwise unit keeps in flight per iteration.
 
     Large streams need ~48 KiB in flight per SM to cover HBM latency (8 chunks x 192 threads x 32 B);
     small ones keep more blocks busy with less unrolling.
     """
     if total >= SM_COUNT * THREADS * 8 * 8:
-        return 8
+        return 8 if streams <= 2 else 4          # more tensors per element: fewer chunks, same bytes in flight
     if total >= SM_COUNT * THREADS * 8 * 2:
         return 2
     return 1
@@ -639,6 +639,27 @@ class Planner:
         if not self._assign_stages(units, writer, ordering):
             raise ValueError("trainkernel: cyclic stage constraints")
 
+        # Streams that depend on nothing but program inputs (the BF16 weight shadows) run as late as
+        # their first consumer allows, in a stage that has tensor-core GEMMs, where the epilogue warps
+        # execute them in the background instead of in a stage of their own.
+        tensor_stages = {u.stage for u in units if u.kind == "gemm" and u.path == "tc"}
+        for unit in units:
+            if unit.kind != "point" or any(buffer in writer for buffer in unit.reads):
+                continue
+            consumers = [u.stage for u in units if u is not unit and unit.writes & u.reads]
+            if not consumers:
+                continue
+            target = min(consumers) - 1
+            while target > unit.stage and target not in tensor_stages:
+                target -= 1
+            limit = min((after.stage for before, after in ordering if before is unit), default=target + 1)
+            if unit.stage < target < limit:
+                unit.stage = target
+        occupied = sorted({u.stage for u in units})
+        renumber = {old: new for new, old in enumerate(occupied)}
+        for unit in units:
+            unit.stage = renumber[unit.stage]
+
         # cross-rank ordering: pulls and reads of pushed results wait for the peers' previous barrier
         remote = {u.root.output.buffer for u in units if u.kind == "exchange"}
         signal: set[int] = set()
@@ -864,4 +885,4 @@ class Planner:
                 unit.items = outputs * unit.parts
         else:
             total = prod(unit.dims)
-            unit.items = max(1, -(-total // (THREADS * 8 * point_unroll(total))))
+            unit.items = max(1, -(-total // (THREADS * 8 * point_unroll(total, len(unit.reads) + len(unit.stores)))))
