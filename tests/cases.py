@@ -122,6 +122,7 @@ CASES = {
     "linear_module": _linear_module_case,
     "mlp_2cta": mlp_case((512, 1024, 768, 512), 512, two_cta=True),
     "mlp_1cta": mlp_case((512, 1024, 768, 512), 512, two_cta=False),
+    "mlp_2cta_background": mlp_case((512, 1024, 768, 512), 512, two_cta=True, background=True),
     # general subset
     "add_one_inplace": function_case(lambda x: x + 1, [(1000,)], inplace_outputs={0: 0}),
     "partial_reduce": function_case(lambda x: (x.sum((0, 2)), x.mean(1, keepdim=True), x.t().sum(0) if x.dim() == 2 else x.sum()), [(5, 7, 9)]),

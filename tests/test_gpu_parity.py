@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 
 GEMM_CASES = [name for name in cases.CASES if name.startswith(("gemm_", "gemm2_", "gemv_"))]
 STEP_CASES = ["c1", "c2", "c2_nofuse", "c2_notc", "c3", "c4", "gemv", "mlp_f32", "mlp_bf16", "mlp_f16",
-              "mlp_f32_one_block", "linear_module", "mlp_2cta", "mlp_1cta"]
+              "mlp_f32_one_block", "linear_module", "mlp_2cta", "mlp_1cta", "mlp_2cta_background"]
 GENERAL_CASES = ["partial_reduce", "big_reduce", "long_reduce", "views_out"]
 
 

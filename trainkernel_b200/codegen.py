@@ -114,7 +114,7 @@ class _Emitter:
         self.needs_simt = False
         self.raster_group = 8
         self.rows = False
-        self.background = True
+        self.background = plan.background
 
     # -- addressing ------------------------------------------------------------------
     def pointer(self, buffer: str, dtype: str, const: bool) -> str:
@@ -771,7 +771,8 @@ def _check_broadcasts(program: Program) -> None:
 
 def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = None, fuse_pointwise: bool = True,
                  fuse_epilogues: bool = True, max_blocks: int | None = None, tensor_cores: bool = True,
-                 block_n: int | None = None, two_cta: bool | None = None, world: int = 1) -> Plan:
+                 block_n: int | None = None, two_cta: bool | None = None, world: int = 1,
+                 background: bool = False) -> Plan:
     """Validate, canonicalise and plan `program` (no code is emitted)."""
     validate(program)
     from .passes import canonicalize_transposed_mm
@@ -799,7 +800,8 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
         if output.buffer not in produced:
             raise ValueError("trainkernel: inplace outputs must be computed values, not input views")
     return Planner(program, inplace_outputs=mapping, fuse_pointwise=fuse_pointwise, fuse_epilogues=fuse_epilogues,
-                   max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n, two_cta=two_cta, world=world).plan()
+                   max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n, two_cta=two_cta, world=world,
+                   background=background).plan()
 
 
 _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shared_skew", "split_k_gemv",
@@ -809,7 +811,7 @@ _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shar
 def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: bool = True,
              max_blocks: int | None = None, inplace_outputs: dict[int, int] | None = None,
              tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
-             two_cta: bool | None = None, raster_group: int | None = None, world: int = 1,
+             two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
              **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
@@ -817,6 +819,11 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     `gemm_tile_n`, `shared_skew`, `split_k_gemv`, `threads_per_block`,
     `inline_input_casts`) have no meaning on this back end; they are accepted so
     existing call sites keep working, and ignored.  `hopper_wgmma=True` is rejected.
+
+    `background=True` lets the epilogue warps of tensor-core stages execute that stage's flat
+    pointwise and exchange units while they wait for the tensor pipe (and places weight-shadow
+    casts next to the GEMM before their first use).  Measured on B200 it did not pay off — one warp
+    per piece keeps too few loads in flight and delays the epilogues — so it is off by default.
     """
     if reference_knobs.pop("hopper_wgmma", False):
         raise ValueError("trainkernel: hopper_wgmma is an SM90a option; this back end targets sm_100a")
@@ -828,7 +835,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         raise ValueError("trainkernel: blocks_per_sm must be between 1 and 8")
     plan = plan_program(program, inplace_outputs=inplace_outputs, fuse_pointwise=fuse_pointwise,
                         fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n,
-                        two_cta=two_cta, world=world)
+                        two_cta=two_cta, world=world, background=background)
     emitter = _Emitter(plan)
     if raster_group is not None:
         if type(raster_group) is not int or not 1 <= raster_group <= 64:

@@ -169,12 +169,13 @@ class Plan:
     world: int = 1
     symmetric_bytes: int = 0
     signal_barriers: tuple = ()            # grid barriers after which this rank raises its flag at every peer
+    background: bool = False               # run memory-bound units inside the epilogue warps of tensor-core stages
 
 
 class Planner:
     def __init__(self, program: Program, *, inplace_outputs: dict[int, int] | None = None,
                  fuse_pointwise: bool = True, fuse_epilogues: bool = True, max_blocks: int | None = None,
-                 tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None, world: int = 1):
+                 tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None, world: int = 1, background: bool = False):
         self.program = program
         self.inplace = dict(inplace_outputs or {})
         self.fuse_pointwise = fuse_pointwise
@@ -184,6 +185,7 @@ class Planner:
         self.forced_block_n = block_n
         self.two_cta = two_cta
         self.world = world
+        self.background = background
         self.ops = list(program.operations)
         self.index = {op.output.buffer: i for i, op in enumerate(self.ops)}
         self.producer = {op.output.buffer: op for op in self.ops}
@@ -642,7 +644,7 @@ class Planner:
         # Streams that depend on nothing but program inputs (the BF16 weight shadows) run as late as
         # their first consumer allows, in a stage that has tensor-core GEMMs, where the epilogue warps
         # execute them in the background instead of in a stage of their own.
-        tensor_stages = {u.stage for u in units if u.kind == "gemm" and u.path == "tc"}
+        tensor_stages = {u.stage for u in units if u.kind == "gemm" and u.path == "tc"} if self.background else set()
         for unit in units:
             if unit.kind != "point" or any(buffer in writer for buffer in unit.reads):
                 continue
@@ -724,7 +726,7 @@ class Planner:
             grid = max(2, grid - grid % 2)
         return Plan(program, sorted(units, key=lambda u: (u.stage, u.index)), stage_count, storage, dtypes, shapes,
                     max(total, ALIGN), inlined, direct, staged, native, grid, tc_units, tc_units > 0, two_cta,
-                    self.world, symmetric if symmetric > SYM_HEADER else 0, tuple(sorted(signal)))
+                    self.world, symmetric if symmetric > SYM_HEADER else 0, tuple(sorted(signal)), self.background)
 
     # -- helpers ---------------------------------------------------------------------
     def _refs(self, expr) -> set[str]:
