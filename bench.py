@@ -35,8 +35,9 @@ if str(ROOT) not in sys.path:
 MEDIUM_SIZES = (4096, 8192, 8192, 8192, 4096)
 MEDIUM_BATCH = 8192
 # DRAM bytes of one medium-MLP step kernel at N = 1 (ncu dram__bytes_read.sum + dram__bytes_write.sum,
-# one-pass capture of the full-size launch; see profiles/tk_step_c5_medium_mlp.md).
-MEASURED_TRAFFIC_BYTES = 14.52e9
+# one-pass capture of the full-size launch of the --single-cta variant, the one ncu is able to launch;
+# see profiles/tk_step_c5_medium_mlp.md).
+MEASURED_TRAFFIC_BYTES = 15.87e9
 
 
 def _peaks() -> dict:
@@ -239,6 +240,9 @@ def main() -> None:
     parser.add_argument("--workload", default="c5", choices=["c5", "c5_half"],
                         help="c5_half (2048-4096-4096-4096-2048, batch 4096) is the small case used for ncu captures")
     parser.add_argument("--eager", action="store_true", help="launch the timed steps directly instead of replaying a CUDA graph")
+    parser.add_argument("--single-cta", action="store_true",
+                        help="generate the kernel with cta_group::1 128x256 tiles instead of two-CTA pair tiles "
+                             "(the variant ncu can profile: ncu fails to launch the clustered cooperative kernel)")
     parser.add_argument("--dp", default="fused", choices=["fused", "nccl"],
                         help="N > 1: gradient exchange inside the step kernel over NVLink peer memory (fused), or "
                              "gradient kernel -> NCCL all-reduce -> update kernel (nccl, the measured baseline)")
@@ -273,7 +277,7 @@ def main() -> None:
     state = work.state
     x0, t0 = work.batches[0]
     if world == 1:
-        step = tk.compile_training(work.fn(), (state, x0, t0))
+        step = tk.compile_training(work.fn(), (state, x0, t0), **({"two_cta": False} if args.single_cta else {}))
         kernels_per_step = 1
         status = step.runner.status
         generated = step.runner.generated
