@@ -64,6 +64,9 @@ def _allreduce_mean(op: Operation, args: list) -> torch.Tensor:
 
 
 _EAGER["allreduce"] = _allreduce_mean
+# index helpers behind `one_hot(labels, C)` written inside a step (not in the reference's operator set)
+_EAGER["eq"] = lambda op, a: torch.eq(a[0], a[1])
+_EAGER["arange"] = lambda op, a: torch.arange(op.attrs["end"])
 
 
 def run(program: Program, inputs: Sequence[torch.Tensor]) -> tuple[torch.Tensor, ...]:
@@ -76,6 +79,8 @@ def run(program: Program, inputs: Sequence[torch.Tensor]) -> tuple[torch.Tensor,
         out_dtype = getattr(torch, op.output.dtype)
         if op.op == "full":
             value = torch.full(op.output.shape, op.attrs["value"], dtype=out_dtype, device=device)
+        elif op.op == "arange":
+            value = torch.arange(op.attrs["end"], dtype=out_dtype, device=device)
         elif op.op in _EAGER:
             operands = [_window(env, x) if isinstance(x, TensorSpec) else x for x in op.inputs]
             value = _EAGER[op.op](op, operands)

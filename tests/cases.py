@@ -65,6 +65,14 @@ def function_case(fn, shapes, dtype=F32, kind="compile", **options):
     return build
 
 
+def _onehot_labels_case(device):
+    """C3 with integer class labels: the one-hot target is formed inside the step."""
+    work = workloads.build("c3", seed=0, device=device)
+    features, _ = work.batches[0]
+    fn = lambda w, x, labels: workloads.onehot_label_step(w, x, labels, 1e-2)  # noqa: E731
+    return fn, (work.state, features, work.labels.to(device)), "compile_training", {}
+
+
 def _linear_module_case(device):
     torch.manual_seed(0)
     model = torch.nn.Sequential(torch.nn.Linear(11, 17), torch.nn.ReLU(), torch.nn.Linear(17, 5)).to(device)
@@ -112,6 +120,7 @@ CASES = {
     "c2_nofuse": workload_case("c2", fuse_epilogues=False, fuse_pointwise=False),
     "c2_notc": workload_case("c2", tensor_cores=False),
     "c3": workload_case("c3"),
+    "c3_labels": _onehot_labels_case,
     "c4": workload_case("c4"),
     "gemv": workload_case("gemv"),
     # the reference's irregular MLP shapes in each dtype

@@ -168,3 +168,20 @@ def test_compile_without_gpu_fails_loudly():
         pytest.skip("a GPU is present")
     with pytest.raises(RuntimeError, match="CUDA sm_100a GPU required"):
         tk.compile(lambda x: x + 1, (torch.ones(4),))
+
+
+def test_integer_labels_flow_only_through_one_hot():
+    work = workloads.build("c3")
+    features, dense = work.batches[0]
+    fn = lambda w, x, labels: workloads.onehot_label_step(w, x, labels, 1e-2)  # noqa: E731
+    program, _ = tk.capture(fn, (work.state, features, work.labels))
+    assert program.inputs[2].dtype == "int64"
+    assert {"arange", "eq"} <= {op.op for op in program.operations}
+    got = run(program, (work.state, features, work.labels))
+    want = run(tk.capture(work.fn(), (work.state, features, dense))[0], (work.state, features, dense))
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)                       # label form == dense one-hot form, bit for bit
+    g = generate(program, inplace_outputs={2: 0})
+    assert g.tensor_core_operations == 2 and "==" in g.source
+    with pytest.raises(ValueError, match="unsupported dtype"):
+        tk.capture(lambda x: x + 1, (torch.ones(3, dtype=torch.int64),))

@@ -9,7 +9,7 @@ from tests.helpers import REL_TOL, assert_outputs_close, assert_step_close, comp
 pytestmark = pytest.mark.gpu
 
 GEMM_CASES = [name for name in cases.CASES if name.startswith(("gemm_", "gemm2_", "gemv_"))]
-STEP_CASES = ["c1", "c2", "c2_nofuse", "c2_notc", "c3", "c4", "gemv", "mlp_f32", "mlp_bf16", "mlp_f16",
+STEP_CASES = ["c1", "c2", "c2_nofuse", "c2_notc", "c3", "c3_labels", "c4", "gemv", "mlp_f32", "mlp_bf16", "mlp_f16",
               "mlp_f32_one_block", "linear_module", "mlp_2cta", "mlp_1cta", "mlp_2cta_background"]
 GENERAL_CASES = ["partial_reduce", "big_reduce", "long_reduce", "views_out"]
 
@@ -172,3 +172,19 @@ def test_fused_exchange_step_with_one_rank_matches_oracle_and_replays():
     step.status()
     assert any(not torch.equal(a, b) for a, b in zip(before, work.state))
     assert all(bool(torch.isfinite(p).all()) for p in work.state)
+
+
+def test_label_indexing_is_bit_exact_with_the_dense_one_hot_target():
+    """`col == label` evaluated in the GEMM epilogue equals one_hot(labels, C) exactly: loss, gradient and
+    updated weights of the label form and of the dense-target form are bit-identical for several steps."""
+    dense, dense_inputs, _, _ = compile_case("c3")
+    labelled, label_inputs, _, _ = compile_case("c3_labels")
+    assert any(op.op == "eq" for op in labelled.program.operations)
+    w_dense, w_label = dense_inputs[0], label_inputs[0]
+    assert torch.equal(w_dense, w_label)
+    for _ in range(5):
+        a = dense(w_dense, *dense_inputs[1:])
+        b = labelled(w_label, *label_inputs[1:])
+        dense.runner.status()
+        labelled.runner.status()
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(w_dense, w_label)

@@ -18,10 +18,10 @@ from dataclasses import dataclass, field
 from math import prod
 
 from .ir import Operation, Program, TensorSpec, row_major, validate
-from .plan import (ELEMENT_BYTES, THREADS, Access, Apply, Const, Load, Plan, Planner, Ref, Unit, point_unroll)
+from .plan import (ELEMENT_BYTES, THREADS, Access, Apply, Const, Iota, Load, Plan, Planner, Ref, Unit, point_unroll)
 
-CTYPE = {"float32": "float", "float16": "__half", "bfloat16": "__nv_bfloat16"}
-ROUND = {"float32": "tk::F32", "float16": "tk::F16", "bfloat16": "tk::BF16"}
+CTYPE = {"float32": "float", "float16": "__half", "bfloat16": "__nv_bfloat16", "int64": "long long", "int32": "int", "bool": "bool"}
+ROUND = {"float32": "tk::F32", "float16": "tk::F16", "bfloat16": "tk::BF16", "int64": "tk::I64", "int32": "tk::I32", "bool": "tk::B8"}
 
 
 def contiguous_strides(shape: tuple[int, ...]) -> tuple[int, ...]:
@@ -175,6 +175,15 @@ class _Emitter:
             body.emit(f"{self._loop(width)} {name}{self._at} = {_literal(expr.value)};")
             env[key] = name
             return name
+        if isinstance(expr, Iota):
+            name = body.temp("i")
+            rank = len(coords)
+            along = expr.dim is not None and (expr.dim == vdim or expr.dim == vdim + rank)
+            start = coords[expr.dim] if expr.dim is not None else "0"
+            body.emit(self._decl(name, width))
+            body.emit(f"{self._loop(width)} {name}{self._at} = (float)(({start}) + {'j' if along else '0'});")
+            env[key] = name
+            return name
         if isinstance(expr, Load):
             access = expr.access
             cache_key = ("load", access)
@@ -232,6 +241,10 @@ class _Emitter:
         if kind == "full":
             return _literal(op.attrs.get("value", op.inputs[0] if op.inputs else 0))
         if kind == "cast":
+            return a[0]
+        if kind == "eq":
+            return f"(({a[0]} == {a[1]}) ? 1.0f : 0.0f)"
+        if kind == "arange":
             return a[0]
         raise ValueError(f"trainkernel: unsupported pointwise operation {kind}")
 

@@ -260,6 +260,17 @@ struct F32 { using T = float; static __device__ __forceinline__ float rnd(float 
 struct BF16 { using T = __nv_bfloat16; static __device__ __forceinline__ float rnd(float x) { return __bfloat162float(__float2bfloat16_rn(x)); } };
 struct F16 { using T = __half; static __device__ __forceinline__ float rnd(float x) { return __half2float(__float2half_rn(x)); } };
 
+// Index dtypes (class labels and what one_hot derives from them) are carried as FP32 inside
+// expressions; exact for magnitudes below 2^24.
+struct I64 { using T = long long; static __device__ __forceinline__ float rnd(float x) { return x; } };
+struct I32 { using T = int; static __device__ __forceinline__ float rnd(float x) { return x; } };
+struct B8 { using T = bool; static __device__ __forceinline__ float rnd(float x) { return x != 0.0f ? 1.0f : 0.0f; } };
+__device__ __forceinline__ float to_f32(long long x) { return static_cast<float>(x); }
+__device__ __forceinline__ float to_f32(int x) { return static_cast<float>(x); }
+__device__ __forceinline__ float to_f32(bool x) { return x ? 1.0f : 0.0f; }
+__device__ __forceinline__ void from_f32(long long* p, float x) { *p = static_cast<long long>(x); }
+__device__ __forceinline__ void from_f32(int* p, float x) { *p = static_cast<int>(x); }
+__device__ __forceinline__ void from_f32(bool* p, float x) { *p = x != 0.0f; }
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
 __device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
@@ -325,6 +336,15 @@ __device__ __forceinline__ void ld_row16(const T16* p, int nvalid, float* out) {
 template <int W> __device__ __forceinline__ void ld_row(const __nv_bfloat16* p, int nvalid, float* out) { ld_row16<W>(p, nvalid, out); }
 template <int W> __device__ __forceinline__ void ld_row(const __half* p, int nvalid, float* out) { ld_row16<W>(p, nvalid, out); }
 
+template <int W, typename TI>
+__device__ __forceinline__ void ld_row_index(const TI* p, int nvalid, float* out) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) out[j] = j < nvalid ? to_f32(p[j]) : 0.0f;
+}
+template <int W> __device__ __forceinline__ void ld_row(const long long* p, int nvalid, float* out) { ld_row_index<W>(p, nvalid, out); }
+template <int W> __device__ __forceinline__ void ld_row(const int* p, int nvalid, float* out) { ld_row_index<W>(p, nvalid, out); }
+template <int W> __device__ __forceinline__ void ld_row(const bool* p, int nvalid, float* out) { ld_row_index<W>(p, nvalid, out); }
+
 // Strided variant: element j lives at p[j * step]; step 0 broadcasts one value.
 template <int W, typename T>
 __device__ __forceinline__ void ld_row_strided(const T* p, int64_t step, int nvalid, float* out) {
@@ -383,6 +403,14 @@ __device__ __forceinline__ void st_row16(T16* p, int nvalid, const float* v) {
 }
 template <int W> __device__ __forceinline__ void st_row(__nv_bfloat16* p, int nvalid, const float* v) { st_row16<W>(p, nvalid, v); }
 template <int W> __device__ __forceinline__ void st_row(__half* p, int nvalid, const float* v) { st_row16<W>(p, nvalid, v); }
+template <int W, typename TI>
+__device__ __forceinline__ void st_row_index(TI* p, int nvalid, const float* v) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) if (j < nvalid) from_f32(p + j, v[j]);
+}
+template <int W> __device__ __forceinline__ void st_row(long long* p, int nvalid, const float* v) { st_row_index<W>(p, nvalid, v); }
+template <int W> __device__ __forceinline__ void st_row(int* p, int nvalid, const float* v) { st_row_index<W>(p, nvalid, v); }
+template <int W> __device__ __forceinline__ void st_row(bool* p, int nvalid, const float* v) { st_row_index<W>(p, nvalid, v); }
 
 // Streaming variants for data touched exactly once by the kernel (FP32 masters read by the SGD
 // expression, FP32 gradients and updated state written by it): the .cs policy marks the lines

@@ -23,6 +23,11 @@ from .ir import Operation, Program, TensorSpec, row_major
 R = TypeVar("R")
 
 DTYPE_NAMES = {torch.float32: "float32", torch.float16: "float16", torch.bfloat16: "bfloat16"}
+# Integer class labels are accepted as inputs so that `one_hot(labels, C)` can be written inside the step
+# (the reference only takes a dense one-hot target built outside, reference: trainkernel/frontend.py:150-151
+# and benchmarks/train_loop.py:66-68).  Index dtypes may only flow through arange / eq / casts.
+INDEX_DTYPE_NAMES = {torch.int64: "int64", torch.int32: "int32", torch.bool: "bool"}
+_INDEX_OPS = ("arange", "eq", "cast")
 
 _PERMUTING = ("aten.t.default", "aten.transpose.int", "aten.permute.default")
 _IDENTITY_VIEWS = ("aten.alias.default", "aten.detach.default")
@@ -123,11 +128,11 @@ def _node_signature(node: torch.fx.Node) -> tuple[tuple[int, ...], str]:
     fake = node.meta.get("val")
     if not isinstance(fake, torch.Tensor):
         raise ValueError(f"trainkernel: missing tensor metadata for {node.name}")
-    if fake.dtype not in DTYPE_NAMES:
+    if fake.dtype not in DTYPE_NAMES and fake.dtype not in INDEX_DTYPE_NAMES:
         raise ValueError(f"trainkernel: unsupported dtype {fake.dtype} at {node.name}")
     if not all(isinstance(extent, int) for extent in fake.shape):
         raise ValueError("trainkernel: dynamic shapes are unsupported")
-    return tuple(fake.shape), DTYPE_NAMES[fake.dtype]
+    return tuple(fake.shape), DTYPE_NAMES.get(fake.dtype) or INDEX_DTYPE_NAMES[fake.dtype]
 
 
 def _fold_view(node: torch.fx.Node, base: TensorSpec, shape: tuple[int, ...], dtype: str) -> TensorSpec:
@@ -207,6 +212,13 @@ def _lower_call(node: torch.fx.Node, specs: dict[torch.fx.Node, TensorSpec]) -> 
         return "full", (_operand(fill, specs, target),), {"value": fill}
     if kind in ("_to_copy", "clone"):
         return "cast", (tensors[0],), {}
+    if kind == "arange":
+        # only the `arange(end)` that one_hot produces: 0, 1, ..., end - 1
+        if len(node.args) != 1 or not isinstance(node.args[0], int) or node.kwargs.get("dtype") not in (None, torch.int64):
+            raise ValueError("trainkernel: only arange(end) with integer end is supported")
+        return "arange", (), {"end": int(node.args[0])}
+    if kind == "eq":
+        return "eq", tuple(_operand(arg, specs, target) for arg in node.args[:2]), {}
     raise ValueError(f"trainkernel: unsupported ATen op {target} at {node.name}")
 
 
@@ -221,8 +233,8 @@ def capture(fn: Callable[..., Any], example_inputs: Sequence[Any]) -> tuple[Prog
     leaves, input_tree = tree_flatten(tuple(example_inputs))
     if not leaves or not all(isinstance(leaf, torch.Tensor) for leaf in leaves):
         raise TypeError("trainkernel: example_inputs must contain tensors only and cannot be empty")
-    if not all(leaf.dtype in DTYPE_NAMES for leaf in leaves):
-        raise ValueError("trainkernel: unsupported dtype; expected float32, float16, or bfloat16")
+    if not all(leaf.dtype in DTYPE_NAMES or leaf.dtype in (torch.int64, torch.int32) for leaf in leaves):
+        raise ValueError("trainkernel: unsupported dtype; expected float32, float16, or bfloat16 (int32/int64 for class labels)")
     if not all(leaf.layout == torch.strided for leaf in leaves):
         raise ValueError("trainkernel: only strided tensors are supported")
     if not all(leaf.device == leaves[0].device for leaf in leaves):
@@ -272,6 +284,9 @@ def capture(fn: Callable[..., Any], example_inputs: Sequence[Any]) -> tuple[Prog
                 specs[node] = _fold_view(node, base, shape, dtype)
                 continue
             kind, operands, attrs = _lower_call(node, specs)
+            if dtype in INDEX_DTYPE_NAMES.values() and kind not in _INDEX_OPS:
+                raise ValueError(f"trainkernel: unsupported dtype {node.meta['val'].dtype} at {node.name}; "
+                                 "integer tensors may only feed arange / eq / casts (one-hot labels)")
             result = TensorSpec(node.name, shape, dtype, row_major(shape), node.name)
             specs[node] = result
             operations.append(Operation(node.name, kind, operands, result, attrs))

@@ -23,12 +23,12 @@ from math import prod
 
 from .ir import Operation, Program, TensorSpec, row_major
 
-POINTWISE = frozenset({"add", "sub", "mul", "div", "neg", "relu", "pow", "threshold_backward", "full", "cast"})
+POINTWISE = frozenset({"add", "sub", "mul", "div", "neg", "relu", "pow", "threshold_backward", "full", "cast", "eq", "arange"})
 REDUCE = frozenset({"sum", "mean"})
 GEMM = frozenset({"mm", "addmm"})
 EXCHANGE = frozenset({"allreduce"})
 SYM_HEADER = 4096                      # flag words at the start of the symmetric buffer
-ELEMENT_BYTES = {"float32": 4, "float16": 2, "bfloat16": 2}
+ELEMENT_BYTES = {"float32": 4, "float16": 2, "bfloat16": 2, "int64": 8, "int32": 4, "bool": 1}
 SM_COUNT = 148
 THREADS = 192
 ALIGN = 256
@@ -55,6 +55,12 @@ class Load:
 @dataclass(frozen=True)
 class Const:
     value: float
+
+
+@dataclass(frozen=True)
+class Iota:
+    """The element's own coordinate along unit dim `dim` (what `arange` evaluates to when inlined)."""
+    dim: int | None
 
 
 @dataclass(frozen=True)
@@ -295,6 +301,8 @@ class Planner:
         return Load(access)
 
     def _apply(self, unit: Unit, op: Operation, pmap: tuple, limit: int) -> Apply:
+        if op.op == "arange":
+            return Apply(op, (Iota(pmap[0] if pmap else None),))
         args = []
         for value in op.inputs:
             if isinstance(value, TensorSpec):

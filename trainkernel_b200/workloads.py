@@ -70,6 +70,26 @@ def onehot_head_step(w, features, onehot, lr: float = 1e-2):
     return loss, grad, w - lr * grad
 
 
+def one_hot(labels, classes: int):
+    """`torch.nn.functional.one_hot` spelled as the comparison it decomposes to.
+
+    Inside `torch.func.grad` the library function validates the label range with
+    data-dependent checks that fake-tensor tracing cannot evaluate; this form traces to
+    `unsqueeze`, `arange` and `eq`, and gives the same result for labels in `[0, classes)`.
+    """
+    return labels.unsqueeze(-1) == torch.arange(classes, device=labels.device)
+
+
+def onehot_label_step(w, features, labels, lr: float = 1e-2):
+    """The same head with integer class labels; the one-hot target is formed inside the step."""
+    def loss_fn(weight):
+        logits = features @ weight.to(torch.bfloat16)
+        onehot = one_hot(labels, weight.shape[1]).to(torch.bfloat16)
+        return ((logits.float() - onehot.float()) ** 2).mean()
+    grad, loss = torch.func.grad_and_value(loss_fn)(w)
+    return loss, grad, w - lr * grad
+
+
 @dataclass
 class Workload:
     """One named configuration: a step function, its state and its resident batches."""
