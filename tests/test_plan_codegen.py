@@ -164,11 +164,13 @@ def test_exchange_units_overlap_backward_gemms_and_precede_updates():
     assert consumer.stage == by_name["mm_2_avg"].stage + 1 and consumer.wait_barrier == consumer.stage - 1
     assert by_name["mm_2_avg"].wait_barrier == by_name["mm_2_avg"].stage - 1
     assert set(plan.signal_barriers) == {u.wait_barrier for u in plan.units if u.wait_barrier is not None}
-    assert plan.storage["mm_2"][0] == "sym" and plan.storage["mm_2_avg"][0] == "sym" and plan.symmetric_bytes > 4096
+    # contributions are scattered into the owner's staging area; the mean is laid out like the value
+    assert plan.storage["mm_2"][0] == "scatter" and plan.storage["mm_2_avg"][0] == "sym" and plan.symmetric_bytes > 4096
     assert len(plan.direct_commits) == 4                                           # updates still commit in place
     g = generate(exchanged, inplace_outputs=inplace, world=2)
     assert g.input_count == len(program.inputs) + 1 + 2 and g.world == 2
     assert "tk::exchange_mean<tk::BF16, 2>" in g.source and "tk::dp_signal" in g.source and "tk::dp_wait" in g.source
+    assert "tk::st_row_scatter<W, 2, __nv_bfloat16>" in g.source          # dW epilogue pushes straight to the owner
     assert runtime.build_cubin(g.source)[:4] == b"\x7fELF"
     with pytest.raises(ValueError, match="world"):
         generate(exchanged, inplace_outputs=inplace, world=9)

@@ -125,6 +125,8 @@ class _Emitter:
             return f"reinterpret_cast<const {ctype}*>({raw})" if const else f"reinterpret_cast<{ctype}*>(const_cast<void*>({raw}))"
         if where[0] == "out":
             return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>(P.out[{where[1]}])"
+        if where[0] == "scatter":
+            raise ValueError(f"trainkernel: {buffer} is staged for a cross-rank exchange and cannot be read in place")
         if where[0] == "sym":
             local = f"reinterpret_cast<uint8_t*>(const_cast<void*>(P.in[{len(self.plan.program.inputs)}]))"
             return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>({local} + {where[1]}ULL)"
@@ -266,6 +268,12 @@ class _Emitter:
             if unit.phase == "partial":
                 continue
             address = self._affine(0, dense, coords, False)
+            where = self.plan.storage[store.buffer]
+            if where[0] == "scatter":
+                n_inputs = len(self.plan.program.inputs)
+                body.emit(f"{self._row_loop()}tk::st_row_scatter<{width}, {self.plan.world}, {CTYPE[store.dtype]}>(&P.in[{n_inputs + 1}], {where[1]}ULL, {where[2]}ULL, "
+                          f"reinterpret_cast<const uint32_t*>(P.in[{n_inputs}])[1], {address}, {nvalid}, {env['ref:' + store.buffer]}{self._row});")
+                continue
             storer = "st_row_stream" if store.buffer in self.write_once else "st_row"
             body.emit(f"{self._row_loop()}tk::{storer}<{width}>({self.pointer(store.buffer, store.dtype, False)} + ({address}), {nvalid}, {env['ref:' + store.buffer]}{self._row});")
 
@@ -666,7 +674,7 @@ class _Emitter:
                         op = unit.root
                         source = op.inputs[0].buffer
                         fn.emit(f"tk::exchange_mean_item<{ROUND[op.output.dtype]}, {plan.world}>(c.dp, {peers}, {plan.storage[source][1]}ULL, "
-                                f"{plan.storage[op.output.buffer][1]}ULL, {prod(unit.dims)}LL, it, tid);")
+                                f"{plan.storage[source][2]}ULL, {plan.storage[op.output.buffer][1]}ULL, {prod(unit.dims)}LL, it, tid);")
                     else:
                         self.point_item(unit, fn, "tid")
                     self.functors.append(f"// {unit.name} ({unit.kind}) of stage {stage}, one 32-thread slice of item `it`\n"
@@ -695,8 +703,8 @@ class _Emitter:
                     op = unit.root
                     source = op.inputs[0].buffer
                     body.emit(f"// {unit.name}: mean of {source} over {plan.world} rank(s)")
-                    body.emit(f"tk::exchange_mean<{ROUND[op.output.dtype]}, {plan.world}>(c, {peers}, "
-                              f"{plan.storage[source][1]}ULL, {plan.storage[op.output.buffer][1]}ULL, {prod(unit.dims)}LL, {bases[id(unit)]}LL, {unit.items}LL);")
+                    body.emit(f"tk::exchange_mean<{ROUND[op.output.dtype]}, {plan.world}>(c, {peers}, {plan.storage[source][1]}ULL, "
+                              f"{plan.storage[source][2]}ULL, {plan.storage[op.output.buffer][1]}ULL, {prod(unit.dims)}LL, {bases[id(unit)]}LL, {unit.items}LL);")
                 elif unit.kind == "gemm":
                     body.emit(f"// {unit.name}: {unit.root.op} {unit.mnk} via {unit.path}")
                     self.gemm(unit, body, bases[id(unit)], bg if unit.path in ("tc", "tc2") else "tk::NoBg")

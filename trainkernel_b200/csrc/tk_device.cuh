@@ -498,8 +498,9 @@ __device__ __forceinline__ void tile_coords(int64_t t, int tiles_m, int tiles_n,
 // barrier that peers care about, ONE thread of the rank stores the current epoch into that word of
 // every rank's header with release semantics at system scope; everything the rank wrote before the
 // barrier (to its own or to a peer's memory) is then visible to whoever acquires the word.  Waits
-// are bounded like every other wait in this file.  Peers are only ever read with plain or relaxed
-// loads and written with plain stores: no multicast, no TMA on remote memory.
+// are bounded like every other wait in this file.  Peer memory is only ever WRITTEN (plain stores:
+// contributions into the owner's staging area, means into every rank's result region) and never
+// read: no remote loads, no multicast, no TMA on remote memory.
 // ----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) { uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory"); }
@@ -554,13 +555,37 @@ __device__ __forceinline__ void dp_wait(Ctx& c, const Dp& d, int world, int barr
 __device__ __forceinline__ void dp_finish(const Dp& d) { st_relaxed_gpu(d.flags, d.epoch); }
 
 // Mean over ranks of a dense value, rounded to T: chunk c (THREADS x 16 bytes) is reduced by rank
-// c % WORLD, which pulls the chunk from every rank (fixed order, FP32 sum), scales by 1/WORLD,
-// rounds, and stores the result into every rank's result region.  Every rank ends up with the
+// c % WORLD, which reads every rank's contribution from its own staging area (filled by
+// st_row_scatter; fixed order, FP32 sum), scales by 1/WORLD, rounds, and stores the result into
+// every rank's result region.  Every rank ends up with the
 // bit-identical mean.  `items` and `item_base` follow the unit conventions (one item = 8 owned chunks).
+// Store `nvalid` of W consecutive elements of a value that is about to be averaged across ranks, starting at
+// flat element index e, into the staging area of the rank that owns their chunk: chunk c = e / (THREADS * VEC)
+// belongs to rank c % WORLD and is staged there at [this rank][c / WORLD].  Producers (GEMM epilogues,
+// reduction finishes) call this instead of a local store, so the contribution crosses NVLink as posted
+// writes while the producing stage runs and nobody ever reads remote memory.
+template <int W, int WORLD, typename T>
+__device__ __forceinline__ void st_row_scatter(const void* const* peers, uint64_t region_offset, uint64_t owned_bytes,
+                                               uint32_t rank, int64_t e, int nvalid, const float* v) {
+    constexpr int64_t chunk = static_cast<int64_t>(kThreads) * (16 / static_cast<int>(sizeof(T)));
+    if (nvalid <= 0) return;
+    if ((e % W) == 0 && (chunk % W) == 0) {                    // the run lies inside one chunk
+        const int64_t c = e / chunk;
+        char* base = reinterpret_cast<char*>(const_cast<void*>(peers[c % WORLD])) + region_offset + rank * owned_bytes;
+        st_row<W>(reinterpret_cast<T*>(base) + (c / WORLD) * chunk + e % chunk, nvalid, v);
+        return;
+    }
+    for (int j = 0; j < W && j < nvalid; ++j) {
+        const int64_t c = (e + j) / chunk;
+        char* base = reinterpret_cast<char*>(const_cast<void*>(peers[c % WORLD])) + region_offset + rank * owned_bytes;
+        from_f32(reinterpret_cast<T*>(base) + (c / WORLD) * chunk + (e + j) % chunk, v[j]);
+    }
+}
+
 constexpr int kExchangeChunksPerItem = 8;
 
 template <typename R, int WORLD>
-__device__ __noinline__ void exchange_mean_item(const Dp& d, const void* const* peers, uint64_t src_offset,
+__device__ __noinline__ void exchange_mean_item(const Dp& d, const void* const* peers, uint64_t src_offset, uint64_t owned_bytes,
                                                    uint64_t dst_offset, int64_t numel, int64_t it, int tid) {
     using T = typename R::T;
     constexpr int VEC = 16 / static_cast<int>(sizeof(T));
@@ -570,19 +595,23 @@ __device__ __noinline__ void exchange_mean_item(const Dp& d, const void* const* 
     // G chunks are pulled together so that G * WORLD 128-bit loads per thread are in flight: a remote
     // load takes a few microseconds, and NVLink only fills up with megabytes outstanding per GPU.
     constexpr int G = WORLD <= 2 ? 8 : (WORLD <= 4 ? 4 : 2);
+    // every rank's contribution to the chunks this rank owns has been staged in LOCAL memory by its producer
+    const char* staging = reinterpret_cast<const char*>(peers[d.rank]) + src_offset;
     {
 #pragma unroll 1
         for (int u0 = 0; u0 < kExchangeChunksPerItem; u0 += G) {
             uint4 raw[G][WORLD];
             int64_t e0[G];
+            const char* staged[G];
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                const int64_t owned = (it * kExchangeChunksPerItem + u0 + g) * WORLD + d.rank;
+                const int64_t slot = it * kExchangeChunksPerItem + u0 + g;           // this rank's slot-th owned chunk
+                const int64_t owned = slot * WORLD + d.rank;
                 e0[g] = owned < chunks ? owned * chunk + static_cast<int64_t>(tid) * VEC : numel;
+                staged[g] = staging + (slot * chunk + static_cast<int64_t>(tid) * VEC) * sizeof(T);
                 if (e0[g] + VEC <= numel) {
 #pragma unroll
-                    for (int j = 0; j < WORLD; ++j)
-                        raw[g][j] = ld_relaxed_sys_v4(reinterpret_cast<const char*>(peers[j]) + src_offset + static_cast<uint64_t>(e0[g]) * sizeof(T));
+                    for (int j = 0; j < WORLD; ++j) raw[g][j] = ld_relaxed_sys_v4(staged[g] + j * owned_bytes);
                 }
             }
 #pragma unroll
@@ -609,7 +638,7 @@ __device__ __noinline__ void exchange_mean_item(const Dp& d, const void* const* 
                     for (int64_t e = e0[g]; e < numel; ++e) {
                         float sum = 0.0f;
                         for (int j = 0; j < WORLD; ++j)
-                            sum += to_f32(ld_volatile<T>(reinterpret_cast<const char*>(peers[j]) + src_offset + e * sizeof(T)));
+                            sum += to_f32(ld_volatile<T>(staged[g] + j * owned_bytes + (e - e0[g]) * sizeof(T)));
                         T value;
                         from_f32(&value, sum * scale);
                         for (int j = 0; j < WORLD; ++j)
@@ -622,10 +651,10 @@ __device__ __noinline__ void exchange_mean_item(const Dp& d, const void* const* 
 }
 
 template <typename R, int WORLD>
-__device__ __forceinline__ void exchange_mean(Ctx& c, const void* const* peers, uint64_t src_offset, uint64_t dst_offset,
-                                              int64_t numel, int64_t item_base, int64_t items) {
+__device__ __forceinline__ void exchange_mean(Ctx& c, const void* const* peers, uint64_t src_offset, uint64_t owned_bytes,
+                                              uint64_t dst_offset, int64_t numel, int64_t item_base, int64_t items) {
     for (int64_t it = first_item(item_base); it < items && !c.aborted(); it += gridDim.x)
-        exchange_mean_item<R, WORLD>(c.dp, peers, src_offset, dst_offset, numel, it, threadIdx.x);
+        exchange_mean_item<R, WORLD>(c.dp, peers, src_offset, owned_bytes, dst_offset, numel, it, threadIdx.x);
 }
 
 // ----------------------------------------------------------------------------

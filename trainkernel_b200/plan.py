@@ -561,12 +561,20 @@ class Planner:
             if unit.kind != "exchange":
                 continue
             source = unit.root.inputs[0].buffer
-            size = -(-max(1, prod(shapes[source])) * ELEMENT_BYTES[dtypes[source]] // ALIGN) * ALIGN
-            for buffer in (source, unit.root.output.buffer):
+            result = unit.root.output.buffer
+            element = ELEMENT_BYTES[dtypes[source]]
+            chunk = THREADS * 16                                   # bytes per exchange chunk
+            chunks = -(-max(1, prod(shapes[source])) * element // chunk)
+            owned = -(-chunks // self.world) * chunk               # bytes one rank receives from one source rank
+            for buffer in (source, result):
                 if buffer in storage:
                     raise ValueError("trainkernel: an exchanged value cannot also be an input or an exchange result")
-                storage[buffer] = ("sym", symmetric)
-                symmetric += size
+            # contributions are scattered by their producers straight into the owning rank's staging area,
+            # laid out [source rank][owned chunk]; the mean is laid out like the value itself
+            storage[source] = ("scatter", symmetric, owned)
+            symmetric += -(-self.world * owned // ALIGN) * ALIGN
+            storage[result] = ("sym", symmetric)
+            symmetric += -(-max(1, prod(shapes[source])) * element // ALIGN) * ALIGN
         native: dict[int, str] = {}
         copies: list[tuple[int, TensorSpec]] = []
         direct_candidates: dict[int, int] = {}
