@@ -155,8 +155,10 @@ class FusedShardedTrainingStep:
     `passes.insert_gradient_exchange` puts an `allreduce` (mean over ranks) behind the loss and
     behind every gradient; the planner turns each into an exchange unit that shares a stage with
     the next backward GEMMs.  The exchanged values live in a peer-mapped buffer allocated through
-    `torch.distributed._symmetric_memory`; chunk c of a value is reduced by rank c % world, which
-    pulls the chunk from every rank over NVLink, and pushes the mean back into every rank's buffer.
+    `torch.distributed._symmetric_memory`; chunk c of a value is owned by rank c % world: every
+    rank's producer (the dW GEMM epilogue, a reduction finish) writes its contribution to that chunk
+    straight into the owner's staging area over NVLink, the owner sums the staged contributions from
+    its own memory and pushes the mean into every rank's buffer.  Remote memory is only written.
     Ranks order themselves with epoch flags stored into each other's buffer after grid barriers.
     All ranks must launch the step the same number of times; state is updated in place and the
     returned loss and gradients are the cross-rank means (buffers owned by this object).
