@@ -73,6 +73,13 @@ def _onehot_labels_case(device):
     return fn, (work.state, features, work.labels.to(device)), "compile_training", {}
 
 
+def _addmm_nan_bias_case(device):
+    """beta = 0 must ignore the bias entirely, NaN included (reference: tests/test_gpu.py:79-86)."""
+    bias = torch.full((40,), float("nan"), device=device)
+    a, b = _rand((24, 56), F32, device, 21), _rand((56, 40), F32, device, 22)
+    return (lambda c, x, y: torch.addmm(c, x, y, beta=0, alpha=2.0)), (bias, a, b), "compile", {}
+
+
 def _linear_module_case(device):
     torch.manual_seed(0)
     model = torch.nn.Sequential(torch.nn.Linear(11, 17), torch.nn.ReLU(), torch.nn.Linear(17, 5)).to(device)
@@ -133,6 +140,9 @@ CASES = {
     "mlp_1cta": mlp_case((512, 1024, 768, 512), 512, two_cta=False),
     "mlp_2cta_background": mlp_case((512, 1024, 768, 512), 512, two_cta=True, background=True),
     # general subset
+    "addmm_scaled": function_case(lambda c, a, b: torch.relu(torch.addmm(c, a, b, beta=0.5, alpha=-1.5)), [(40,), (24, 56), (56, 40)]),
+    "addmm_scaled_bf16": function_case(lambda c, a, b: torch.addmm(c, a, b, beta=2.0, alpha=0.25), [(136, 72), (136, 200), (200, 72)], BF16),
+    "addmm_beta0_nan_bias": _addmm_nan_bias_case,
     "add_one_inplace": function_case(lambda x: x + 1, [(1000,)], inplace_outputs={0: 0}),
     "partial_reduce": function_case(lambda x: (x.sum((0, 2)), x.mean(1, keepdim=True), x.t().sum(0) if x.dim() == 2 else x.sum()), [(5, 7, 9)]),
     "big_reduce": function_case(lambda x: (x.sum(), x.mean(0)), [(5003, 3)]),
