@@ -76,7 +76,10 @@ def kernel_sources() -> dict[str, str]:
             sources["medium_update"] = codegen.generate(update, inplace_outputs={count + i: i for i in range(count)}).source
         from trainkernel_b200.passes import insert_gradient_exchange
         fused = insert_gradient_exchange(_medium_program(MEDIUM_BATCH // world), count)
-        sources[f"medium_fused_n{world}"] = codegen.generate(fused, inplace_outputs={1 + count + i: i for i in range(count)}, world=world).source
+        for multicast in (False, True):
+            name = f"medium_fused_n{world}" + ("_multicast" if multicast else "")
+            sources[name] = codegen.generate(fused, inplace_outputs={1 + count + i: i for i in range(count)}, world=world,
+                                             multicast=multicast).source
     return sources
 
 
@@ -246,6 +249,9 @@ def main() -> None:
     parser.add_argument("--dp", default="fused", choices=["fused", "nccl"],
                         help="N > 1: gradient exchange inside the step kernel over NVLink peer memory (fused), or "
                              "gradient kernel -> NCCL all-reduce -> update kernel (nccl, the measured baseline)")
+    parser.add_argument("--no-multicast", action="store_true",
+                        help="N > 1, fused: never exchange through the NVSwitch multicast mapping (multimem); "
+                             "contributions are then scattered to their owners with plain peer stores")
     args = parser.parse_args()
     global MEDIUM_SIZES, MEDIUM_BATCH
     if args.workload == "c5_half":
@@ -282,7 +288,7 @@ def main() -> None:
         status = step.runner.status
         generated = step.runner.generated
     elif args.dp == "fused":
-        step = dp.FusedShardedTrainingStep(work.fn(), (state, x0, t0))
+        step = dp.FusedShardedTrainingStep(work.fn(), (state, x0, t0), multicast=False if args.no_multicast else None)
         kernels_per_step = step.kernels_per_step
         status = step.status
         generated = step.generated
@@ -379,7 +385,9 @@ def main() -> None:
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload} medium MLP {'-'.join(map(str, MEDIUM_SIZES))}, global batch {MEDIUM_BATCH}, BF16 compute / FP32 master, SGD lr 1e-3",
                    "global_batch": MEDIUM_BATCH, "rows_per_rank": work.batch, "resident_batches": len(work.batches),
-                   "parallelism": (f"dp{world} (batch-sharded, BF16 gradient mean exchanged inside the step kernel over NVLink peer memory)"
+                   "parallelism": (f"dp{world} (batch-sharded, BF16 gradient mean exchanged inside the step kernel over NVLink, "
+                                   + ("multimem.ld_reduce / multimem.st through the NVSwitch multicast mapping)" if getattr(step, "multicast", False)
+                                      else "peer stores into the owners' staging areas)")
                                    if world > 1 and args.dp == "fused" else
                                    f"dp{world} (batch-sharded, NCCL all-reduce of the BF16 gradients between two kernels)" if world > 1
                                    else "single GPU, one kernel per step"),

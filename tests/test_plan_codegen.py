@@ -174,3 +174,11 @@ def test_exchange_units_overlap_backward_gemms_and_precede_updates():
     assert runtime.build_cubin(g.source)[:4] == b"\x7fELF"
     with pytest.raises(ValueError, match="world"):
         generate(exchanged, inplace_outputs=inplace, world=9)
+    # through the NVSwitch multicast mapping: contributions stay local, one more pointer, no scatter
+    switch = generate(exchanged, inplace_outputs=inplace, world=2, multicast=True)
+    assert switch.multicast and switch.input_count == len(program.inputs) + 1 + 2 + 1
+    assert f"tk::exchange_mean_mc<tk::BF16, 2>(c, &P.in[{len(program.inputs) + 1}], P.in[{len(program.inputs) + 3}]" in switch.source
+    assert "st_row_scatter" not in switch.source and "tk::dp_wait" in switch.source
+    assert switch.symmetric_bytes <= g.symmetric_bytes and switch.stages == g.stages
+    assert runtime.build_cubin(switch.source)[:4] == b"\x7fELF"
+    assert not generate(exchanged, inplace_outputs=inplace, world=1, multicast=True).multicast    # one rank: nothing to exchange through

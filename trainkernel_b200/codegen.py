@@ -78,6 +78,7 @@ class GeneratedKernel:
     workspace_bytes: int = 0
     cluster: int = 1                      # thread-block cluster size the kernel must be launched with
     world: int = 1                        # ranks the kernel exchanges with (1: no exchange stages)
+    multicast: bool = False               # exchanges through the multicast mapping (one more extra input)
     symmetric_bytes: int = 0              # size of the peer-mapped buffer the kernel expects after the program inputs
 
 
@@ -636,6 +637,16 @@ class _Emitter:
         body.emit("}")
 
     # -- whole kernel ------------------------------------------------------------------
+    def _exchange_call(self, unit: Unit, peers: str, suffix: str, context: str, tail: str) -> str:
+        """The device call of an exchange unit: scatter-staged, or through the multicast mapping."""
+        plan, op = self.plan, unit.root
+        source, result = plan.storage[op.inputs[0].buffer], plan.storage[op.output.buffer]
+        head = f"<{ROUND[op.output.dtype]}, {plan.world}>({context}, {peers}, "
+        if plan.multicast:
+            mc = f"P.in[{len(plan.program.inputs) + 1 + plan.world}]"
+            return f"tk::exchange_mean_mc{suffix}{head}{mc}, {source[1]}ULL, {result[1]}ULL, {prod(unit.dims)}LL, {tail});"
+        return f"tk::exchange_mean{suffix}{head}{source[1]}ULL, {source[2]}ULL, {result[1]}ULL, {prod(unit.dims)}LL, {tail});"
+
     def kernel(self, stage_stamps: bool) -> str:
         plan = self.plan
         body = _Body()
@@ -671,10 +682,7 @@ class _Emitter:
                     fn = _Body()
                     fn.depth = 1
                     if unit.kind == "exchange":
-                        op = unit.root
-                        source = op.inputs[0].buffer
-                        fn.emit(f"tk::exchange_mean_item<{ROUND[op.output.dtype]}, {plan.world}>(c.dp, {peers}, {plan.storage[source][1]}ULL, "
-                                f"{plan.storage[source][2]}ULL, {plan.storage[op.output.buffer][1]}ULL, {prod(unit.dims)}LL, it, tid);")
+                        fn.emit(self._exchange_call(unit, peers, "_item", "c.dp", "it, tid"))
                     else:
                         self.point_item(unit, fn, "tid")
                     self.functors.append(f"// {unit.name} ({unit.kind}) of stage {stage}, one 32-thread slice of item `it`\n"
@@ -703,8 +711,7 @@ class _Emitter:
                     op = unit.root
                     source = op.inputs[0].buffer
                     body.emit(f"// {unit.name}: mean of {source} over {plan.world} rank(s)")
-                    body.emit(f"tk::exchange_mean<{ROUND[op.output.dtype]}, {plan.world}>(c, {peers}, {plan.storage[source][1]}ULL, "
-                              f"{plan.storage[source][2]}ULL, {plan.storage[op.output.buffer][1]}ULL, {prod(unit.dims)}LL, {bases[id(unit)]}LL, {unit.items}LL);")
+                    body.emit(self._exchange_call(unit, peers, "", "c", f"{bases[id(unit)]}LL, {unit.items}LL"))
                 elif unit.kind == "gemm":
                     body.emit(f"// {unit.name}: {unit.root.op} {unit.mnk} via {unit.path}")
                     self.gemm(unit, body, bases[id(unit)], bg if unit.path in ("tc", "tc2") else "tk::NoBg")
@@ -718,7 +725,7 @@ class _Emitter:
                 self._drained = stage
                 body.emit(f"tk::bg_drain<{bg}>(c, P);   // whatever background work is left, by all warps")
         exchanging = plan.symmetric_bytes > 0
-        n_in = max(1, len(plan.program.inputs) + (1 + plan.world if exchanging else 0))
+        n_in = max(1, len(plan.program.inputs) + (1 + plan.world + int(plan.multicast) if exchanging else 0))
         n_out = max(1, len(plan.program.outputs))
         n_maps = max(1, len(self.maps))
         n_maps_used = len(self.maps)
@@ -793,7 +800,7 @@ def _check_broadcasts(program: Program) -> None:
 def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = None, fuse_pointwise: bool = True,
                  fuse_epilogues: bool = True, max_blocks: int | None = None, tensor_cores: bool = True,
                  block_n: int | None = None, two_cta: bool | None = None, world: int = 1,
-                 background: bool = False) -> Plan:
+                 background: bool = False, multicast: bool = False) -> Plan:
     """Validate, canonicalise and plan `program` (no code is emitted)."""
     validate(program)
     from .passes import canonicalize_transposed_mm
@@ -822,7 +829,7 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
             raise ValueError("trainkernel: inplace outputs must be computed values, not input views")
     return Planner(program, inplace_outputs=mapping, fuse_pointwise=fuse_pointwise, fuse_epilogues=fuse_epilogues,
                    max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n, two_cta=two_cta, world=world,
-                   background=background).plan()
+                   background=background, multicast=multicast).plan()
 
 
 _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shared_skew", "split_k_gemv",
@@ -833,7 +840,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              max_blocks: int | None = None, inplace_outputs: dict[int, int] | None = None,
              tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
              two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
-             **reference_knobs) -> GeneratedKernel:
+             multicast: bool = False, **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -845,6 +852,11 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     pointwise and exchange units while they wait for the tensor pipe (and places weight-shadow
     casts next to the GEMM before their first use).  Measured on B200 it did not pay off — one warp
     per piece keeps too few loads in flight and delays the epilogues — so it is off by default.
+
+    With `world > 1` the kernel takes `1 + world` extra inputs after the program's own: this rank's
+    symmetric buffer, then every rank's mapping of it in rank order.  `multicast=True` adds one more,
+    this rank's pointer to the NVSwitch multicast mapping of the buffer, and exchanges through
+    `multimem.ld_reduce` / `multimem.st` instead of scattering contributions to their owners.
     """
     if reference_knobs.pop("hopper_wgmma", False):
         raise ValueError("trainkernel: hopper_wgmma is an SM90a option; this back end targets sm_100a")
@@ -856,14 +868,14 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         raise ValueError("trainkernel: blocks_per_sm must be between 1 and 8")
     plan = plan_program(program, inplace_outputs=inplace_outputs, fuse_pointwise=fuse_pointwise,
                         fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n,
-                        two_cta=two_cta, world=world, background=background)
+                        two_cta=two_cta, world=world, background=background, multicast=multicast)
     emitter = _Emitter(plan)
     if raster_group is not None:
         if type(raster_group) is not int or not 1 <= raster_group <= 64:
             raise ValueError("trainkernel: raster_group must be between 1 and 64")
         emitter.raster_group = raster_group
     source = emitter.kernel(stage_stamps)
-    extra_inputs = 1 + plan.world if plan.symmetric_bytes else 0
+    extra_inputs = 1 + plan.world + int(plan.multicast) if plan.symmetric_bytes else 0
     n_in, n_out = max(1, len(plan.program.inputs) + extra_inputs), max(1, len(plan.program.outputs))
     n_maps = max(1, len(emitter.maps))
     param_bytes = 128 * n_maps + 8 * (n_in + n_out) + 8 * 6
@@ -900,5 +912,6 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         workspace_bytes=plan.workspace_bytes,
         cluster=2 if plan.two_cta else 1,
         world=plan.world,
+        multicast=plan.multicast,
         symmetric_bytes=plan.symmetric_bytes,
     )

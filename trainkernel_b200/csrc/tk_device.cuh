@@ -15,6 +15,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
+#include <type_traits>
 
 namespace tk {
 
@@ -554,11 +555,6 @@ __device__ __forceinline__ void dp_wait(Ctx& c, const Dp& d, int world, int barr
 }
 __device__ __forceinline__ void dp_finish(const Dp& d) { st_relaxed_gpu(d.flags, d.epoch); }
 
-// Mean over ranks of a dense value, rounded to T: chunk c (THREADS x 16 bytes) is reduced by rank
-// c % WORLD, which reads every rank's contribution from its own staging area (filled by
-// st_row_scatter; fixed order, FP32 sum), scales by 1/WORLD, rounds, and stores the result into
-// every rank's result region.  Every rank ends up with the
-// bit-identical mean.  `items` and `item_base` follow the unit conventions (one item = 8 owned chunks).
 // Store `nvalid` of W consecutive elements of a value that is about to be averaged across ranks, starting at
 // flat element index e, into the staging area of the rank that owns their chunk: chunk c = e / (THREADS * VEC)
 // belongs to rank c % WORLD and is staged there at [this rank][c / WORLD].  Producers (GEMM epilogues,
@@ -584,6 +580,10 @@ __device__ __forceinline__ void st_row_scatter(const void* const* peers, uint64_
 
 constexpr int kExchangeChunksPerItem = 8;
 
+// Mean over ranks of a dense value, rounded to T: chunk c (THREADS x 16 bytes) is reduced by rank
+// c % WORLD, which reads every rank's contribution from its own staging area (filled by
+// st_row_scatter; fixed order, FP32 sum), scales by 1/WORLD, rounds, and stores the result into
+// every rank's result region.  Every rank ends up with the bit-identical mean.  One item = 8 owned chunks.
 template <typename R, int WORLD>
 __device__ __noinline__ void exchange_mean_item(const Dp& d, const void* const* peers, uint64_t src_offset, uint64_t owned_bytes,
                                                    uint64_t dst_offset, int64_t numel, int64_t it, int tid) {
@@ -655,6 +655,80 @@ __device__ __forceinline__ void exchange_mean(Ctx& c, const void* const* peers, 
                                               uint64_t dst_offset, int64_t numel, int64_t item_base, int64_t items) {
     for (int64_t it = first_item(item_base); it < items && !c.aborted(); it += gridDim.x)
         exchange_mean_item<R, WORLD>(c.dp, peers, src_offset, owned_bytes, dst_offset, numel, it, threadIdx.x);
+}
+
+// The same exchange through the NVSwitch multicast mapping of the symmetric buffer (`mc` is this
+// rank's pointer to it).  Every rank keeps its contribution in its OWN buffer; the owner of a chunk
+// issues one multimem.ld_reduce per 16 bytes, which the switch answers with the FP32-accumulated sum
+// over all ranks (so a chunk crosses this rank's links once, already reduced), scales and rounds
+// it, and one multimem.st delivers the mean to every rank's result region.  Per rank and direction
+// this moves (WORLD - 1) / WORLD + 1 / WORLD of the value instead of 2 (WORLD - 1) / WORLD.
+// The sum comes back rounded to T; scaling by 1 / WORLD afterwards is exact for power-of-two WORLD.
+// Elements of a last, partial 16-byte group go over the unicast peer pointers.
+template <typename T>
+__device__ __forceinline__ uint4 multimem_sum_v4(const void* p) {
+    uint4 v;
+    if constexpr (sizeof(T) == 4)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    else if constexpr (std::is_same<T, __nv_bfloat16>::value)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    else
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void multimem_st_v4(void* p, const uint4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+template <typename R, int WORLD>
+__device__ __noinline__ void exchange_mean_mc_item(const Dp& d, const void* const* peers, const void* mc, uint64_t src_offset,
+                                                      uint64_t dst_offset, int64_t numel, int64_t it, int tid) {
+    using T = typename R::T;
+    static_assert(std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value || std::is_same<T, __half>::value,
+                  "exchanged values are floating point");
+    constexpr int VEC = 16 / static_cast<int>(sizeof(T));
+    constexpr int G = kExchangeChunksPerItem;
+    const int64_t chunk = static_cast<int64_t>(kThreads) * VEC;
+    const int64_t chunks = (numel + chunk - 1) / chunk;
+    const float scale = 1.0f / static_cast<float>(WORLD);
+    char* base = reinterpret_cast<char*>(const_cast<void*>(mc));
+    uint4 raw[G];
+    int64_t e0[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const int64_t owned = (it * G + g) * WORLD + d.rank;
+        e0[g] = owned < chunks ? owned * chunk + static_cast<int64_t>(tid) * VEC : numel;
+        if (e0[g] + VEC <= numel) raw[g] = multimem_sum_v4<T>(base + src_offset + static_cast<uint64_t>(e0[g]) * sizeof(T));
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        if (e0[g] >= numel) continue;
+        if (e0[g] + VEC <= numel) {
+            const T* part = reinterpret_cast<const T*>(&raw[g]);
+            uint4 packed;
+            T* out = reinterpret_cast<T*>(&packed);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) from_f32(out + e, to_f32(part[e]) * scale);
+            multimem_st_v4(base + dst_offset + static_cast<uint64_t>(e0[g]) * sizeof(T), packed);
+        } else {
+            for (int64_t e = e0[g]; e < numel; ++e) {
+                float sum = 0.0f;
+                for (int j = 0; j < WORLD; ++j)
+                    sum += to_f32(ld_volatile<T>(reinterpret_cast<const char*>(peers[j]) + src_offset + e * sizeof(T)));
+                T value;
+                from_f32(&value, sum * scale);
+                for (int j = 0; j < WORLD; ++j)
+                    *reinterpret_cast<T*>(reinterpret_cast<char*>(const_cast<void*>(peers[j])) + dst_offset + e * sizeof(T)) = value;
+            }
+        }
+    }
+}
+
+template <typename R, int WORLD>
+__device__ __forceinline__ void exchange_mean_mc(Ctx& c, const void* const* peers, const void* mc, uint64_t src_offset,
+                                                 uint64_t dst_offset, int64_t numel, int64_t item_base, int64_t items) {
+    for (int64_t it = first_item(item_base); it < items && !c.aborted(); it += gridDim.x)
+        exchange_mean_mc_item<R, WORLD>(c.dp, peers, mc, src_offset, dst_offset, numel, it, threadIdx.x);
 }
 
 // ----------------------------------------------------------------------------

@@ -159,12 +159,23 @@ class FusedShardedTrainingStep:
     rank's producer (the dW GEMM epilogue, a reduction finish) writes its contribution to that chunk
     straight into the owner's staging area over NVLink, the owner sums the staged contributions from
     its own memory and pushes the mean into every rank's buffer.  Remote memory is only written.
+    When the buffer also has an NVSwitch multicast mapping (`multicast=None`: use it from four ranks up if every rank has
+    one; `False`: never; `True`: require it) contributions stay in their rank's own buffer instead:
+    the owner of a chunk reads the in-switch sum with `multimem.ld_reduce` and delivers the mean to all
+    ranks with one `multimem.st`, which halves the bytes each rank's links carry.
     Ranks order themselves with epoch flags stored into each other's buffer after grid barriers.
     All ranks must launch the step the same number of times; state is updated in place and the
     returned loss and gradients are the cross-rank means (buffers owned by this object).
     """
 
-    def __init__(self, fn: Callable[..., Any], example_inputs: Sequence[Any], *, group: Any = None, **options: Any) -> None:
+    # Smallest world size at which the multicast form is preferred when available.  With two ranks it
+    # moves more bytes per link than scattering does (every multimem access also loops through the
+    # switch for the issuing rank's own copy) and its loads are not hidden behind a GEMM; measured on
+    # two B200s the scatter form is 8 % faster per step.
+    MULTICAST_FROM = 4
+
+    def __init__(self, fn: Callable[..., Any], example_inputs: Sequence[Any], *, group: Any = None,
+                 multicast: bool | None = None, **options: Any) -> None:
         from .codegen import generate
         from .passes import insert_gradient_exchange
         if "inplace_outputs" in options or "world" in options:
@@ -181,13 +192,18 @@ class FusedShardedTrainingStep:
         device = self.device = flat[0].device
         self.program = insert_gradient_exchange(program, n)
         verbose = options.pop("verbose", False)
-        self.generated = generate(self.program, inplace_outputs={1 + n + i: i for i in range(n)}, world=self.world, **options)
-        cubin = runtime.build_cubin(self.generated.source, verbose=verbose)
-        with torch.cuda.device(device):
-            torch.cuda.current_stream(device)
-            self.module = runtime._Module(self.generated, cubin, device)
-        # the peer-mapped buffer: header words (epoch, rank, barrier flags) then the exchanged values
+        inplace = {1 + n + i: i for i in range(n)}
+        # The size of the symmetric buffer depends on the exchange form, and whether the multicast form
+        # is available is only known once a buffer has been mapped: plan both, allocate for the larger.
+        self.generated = generate(self.program, inplace_outputs=inplace, world=self.world, **options)
         words = self.generated.symmetric_bytes // 4
+        through_switch = None
+        if multicast is None:
+            multicast = None if self.world >= self.MULTICAST_FROM else False
+        if self.world > 1 and multicast is not False:
+            through_switch = generate(self.program, inplace_outputs=inplace, world=self.world, multicast=True, **options)
+            words = max(words, through_switch.symmetric_bytes // 4)
+        # the peer-mapped buffer: header words (epoch, rank, barrier flags) then the exchanged values
         if self.world > 1:
             import torch.distributed._symmetric_memory as symm_mem
             self.symmetric = symm_mem.empty(words, dtype=torch.int32, device=device)
@@ -197,11 +213,27 @@ class FusedShardedTrainingStep:
             handle = symm_mem.rendezvous(self.symmetric, group if group is not None else dist.group.WORLD)
             self._handle = handle
             peers = [int(p) for p in handle.buffer_ptrs]
+            switch_pointer = int(getattr(handle, "multicast_ptr", 0) or 0)
+            # every rank must take the same form: use the switch only if all ranks got a multicast mapping
+            agreed = torch.tensor([1 if switch_pointer else 0], dtype=torch.int32, device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+            if through_switch is not None and int(agreed.item()):
+                self.generated = through_switch
+            elif multicast:
+                raise RuntimeError("trainkernel: multicast exchange requested but the symmetric buffer has no multicast mapping")
             dist.barrier(group)
         else:
             self.symmetric = torch.zeros(words, dtype=torch.int32, device=device)
             peers = [self.symmetric.data_ptr()]
+            switch_pointer = 0
+        self.multicast = self.generated.multicast
         self._extra = [_Pointer(self.symmetric.data_ptr())] + [_Pointer(p) for p in peers]
+        if self.multicast:
+            self._extra.append(_Pointer(switch_pointer))
+        cubin = runtime.build_cubin(self.generated.source, verbose=verbose)
+        with torch.cuda.device(device):
+            torch.cuda.current_stream(device)
+            self.module = runtime._Module(self.generated, cubin, device)
         self._checker = runtime.CompiledProgram(program, self.generated, self.module, device, {1 + n + i: i for i in range(n)})
         self.loss = torch.zeros((), dtype=torch.float32, device=device)
         self.gradients = tuple(torch.empty(spec.shape, dtype=getattr(torch, spec.dtype), device=device)

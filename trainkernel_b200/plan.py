@@ -176,12 +176,14 @@ class Plan:
     symmetric_bytes: int = 0
     signal_barriers: tuple = ()            # grid barriers after which this rank raises its flag at every peer
     background: bool = False               # run memory-bound units inside the epilogue warps of tensor-core stages
+    multicast: bool = False                # exchange through the NVSwitch multicast mapping (multimem) instead of scattering
 
 
 class Planner:
     def __init__(self, program: Program, *, inplace_outputs: dict[int, int] | None = None,
                  fuse_pointwise: bool = True, fuse_epilogues: bool = True, max_blocks: int | None = None,
-                 tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None, world: int = 1, background: bool = False):
+                 tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None, world: int = 1, background: bool = False,
+                 multicast: bool = False):
         self.program = program
         self.inplace = dict(inplace_outputs or {})
         self.fuse_pointwise = fuse_pointwise
@@ -192,6 +194,7 @@ class Planner:
         self.two_cta = two_cta
         self.world = world
         self.background = background
+        self.multicast = bool(multicast) and world > 1
         self.ops = list(program.operations)
         self.index = {op.output.buffer: i for i, op in enumerate(self.ops)}
         self.producer = {op.output.buffer: op for op in self.ops}
@@ -569,10 +572,16 @@ class Planner:
             for buffer in (source, result):
                 if buffer in storage:
                     raise ValueError("trainkernel: an exchanged value cannot also be an input or an exchange result")
-            # contributions are scattered by their producers straight into the owning rank's staging area,
-            # laid out [source rank][owned chunk]; the mean is laid out like the value itself
-            storage[source] = ("scatter", symmetric, owned)
-            symmetric += -(-self.world * owned // ALIGN) * ALIGN
+            if self.multicast:
+                # every rank keeps its contribution in its own buffer, laid out like the value; the owner of a
+                # chunk fetches the sum over ranks through the multicast mapping
+                storage[source] = ("sym", symmetric)
+                symmetric += -(-max(1, prod(shapes[source])) * element // ALIGN) * ALIGN
+            else:
+                # contributions are scattered by their producers straight into the owning rank's staging area,
+                # laid out [source rank][owned chunk]; the mean is laid out like the value itself
+                storage[source] = ("scatter", symmetric, owned)
+                symmetric += -(-self.world * owned // ALIGN) * ALIGN
             storage[result] = ("sym", symmetric)
             symmetric += -(-max(1, prod(shapes[source])) * element // ALIGN) * ALIGN
         native: dict[int, str] = {}
@@ -742,7 +751,7 @@ class Planner:
             grid = max(2, grid - grid % 2)
         return Plan(program, sorted(units, key=lambda u: (u.stage, u.index)), stage_count, storage, dtypes, shapes,
                     max(total, ALIGN), inlined, direct, staged, native, grid, tc_units, tc_units > 0, two_cta,
-                    self.world, symmetric if symmetric > SYM_HEADER else 0, tuple(sorted(signal)), self.background)
+                    self.world, symmetric if symmetric > SYM_HEADER else 0, tuple(sorted(signal)), self.background, self.multicast)
 
     # -- helpers ---------------------------------------------------------------------
     def _refs(self, expr) -> set[str]:
