@@ -40,3 +40,41 @@ def stage_profile(fn: Callable[..., Any], example_inputs: Sequence[Any], *, trai
         units = [f"{name}:{kind}{'/' + path if path else ''}" for s, kind, name, path, _ in runner.generated.units if s == stage]
         records.append({"stage": stage, "min_us": column[0], "median_us": column[len(column) // 2], "units": units})
     return records
+
+
+def main(argv=None) -> int:
+    """`python -m trainkernel_b200.profile c4` prints the stage table of a named workload as JSON lines.
+
+    `--plain` compiles without stamps and only launches the step `--repeats` times: the command to
+    put under a hardware profiler.
+    """
+    import argparse
+    import json
+
+    from . import workloads
+
+    parser = argparse.ArgumentParser(description=main.__doc__)
+    parser.add_argument("workload", choices=workloads.CONFIG_NAMES)
+    parser.add_argument("--repeats", type=int, default=10)
+    parser.add_argument("--plain", action="store_true")
+    parser.add_argument("--device", default="cuda:0")
+    args = parser.parse_args(argv)
+    work = workloads.build(args.workload, device=args.device)
+    inputs = (work.state, *work.batches[0])
+    if args.plain:
+        compiled = compile_training(work.fn(), inputs)
+        for _ in range(args.repeats):
+            compiled(*inputs)
+        torch.cuda.synchronize()
+        compiled.runner.status()
+        print(json.dumps({"workload": work.name, "launches": args.repeats, "stages": compiled.runner.generated.stages}))
+        return 0
+    records = stage_profile(work.fn(), inputs, repeats=args.repeats)
+    for record in records:
+        print(json.dumps(record))
+    print(json.dumps({"workload": work.name, "stages": len(records), "sum_min_us": sum(r["min_us"] for r in records)}))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
