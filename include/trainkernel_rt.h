@@ -66,9 +66,10 @@ int tk_module_launch(tk_module* module, const void* const* inputs, void* const* 
  * resident blocks per SM}.  Replaces `resource_usage()` (reference: trainkernel/codegen.py:889-895). */
 int tk_module_resource_usage(tk_module* module, int64_t out[4]);
 
-/* Launch the kernel with thread-block clusters of `size` CTAs (1 or 2; kernels generated with the
- * two-CTA tcgen05 GEMM need 2).  Recomputes the co-resident capacity for clustered launches.  New on
- * this back end: the reference's kernels have no cluster dimension (trainkernel/codegen.py:886). */
+/* Launch the kernel with thread-block clusters of `size` CTAs (1, 2, 4 or 8).  Kernels generated with
+ * the two-CTA tcgen05 GEMM need 2; kernels whose stages end in the hardware cluster barrier are
+ * launched as ONE cluster (grid == size).  Recomputes the co-resident capacity for clustered launches.
+ * New on this back end: the reference's kernels have no cluster dimension (trainkernel/codegen.py:886). */
 int tk_module_set_cluster(tk_module* module, int size);
 
 /* Largest grid a cooperative launch of this kernel accepts on its device. */

@@ -124,6 +124,9 @@ CASES = {
     # BASELINE configurations and the batch-1 pin
     "c1": workload_case("c1"),
     "c2": workload_case("c2"),
+    "c1_grid_barrier": workload_case("c1", cluster_barrier=False),
+    "c2_grid_barrier": workload_case("c2", cluster_barrier=False),
+    "c3_one_cluster": workload_case("c3", cluster_barrier=True),
     "c2_nofuse": workload_case("c2", fuse_epilogues=False, fuse_pointwise=False),
     "c2_notc": workload_case("c2", tensor_cores=False),
     "c3": workload_case("c3"),

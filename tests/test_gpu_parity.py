@@ -105,10 +105,10 @@ def test_runtime_rejects_mismatched_inputs_and_aliased_buffers():
 def test_barrier_timeout_is_reported_not_hung():
     """A barrier that can never complete must end with an error status, not a stuck device."""
     from trainkernel_b200 import runtime
-    compiled, inputs, _, _ = compile_case("c1")
+    compiled, inputs, _, _ = compile_case("c1_grid_barrier")
     runner = compiled.runner
     lib = runtime.library()
-    assert runner.module.grid > 1
+    assert runner.module.grid > 1 and runner.generated.barrier == "grid"
     lib.tk_module_set_timeout(runner.module.handle, 20_000_000)               # 20 ms
     lib.tk_module_set_expected_arrivals(runner.module.handle, runner.module.grid + 1)
     state = inputs[0].clone()

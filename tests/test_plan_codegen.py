@@ -182,3 +182,24 @@ def test_exchange_units_overlap_backward_gemms_and_precede_updates():
     assert switch.symmetric_bytes <= g.symmetric_bytes and switch.stages == g.stages
     assert runtime.build_cubin(switch.source)[:4] == b"\x7fELF"
     assert not generate(exchanged, inplace_outputs=inplace, world=1, multicast=True).multicast    # one rank: nothing to exchange through
+
+
+def test_small_programs_run_as_one_cluster_with_the_hardware_barrier():
+    program, inplace = _step_program("c2")
+    g = generate(program, inplace_outputs=inplace)
+    assert g.barrier == "cluster" and g.grid == g.cluster == 8
+    assert "tk::cluster_barrier(c);" in g.source and "tk::grid_barrier(c);" not in g.source
+    wide = generate(program, inplace_outputs=inplace, cluster_barrier=False)
+    assert wide.barrier == "grid" and wide.cluster == 1 and wide.grid > 8 and "tk::grid_barrier(c);" in wide.source
+    one = generate(program, inplace_outputs=inplace, max_blocks=1)
+    assert one.barrier == "cluster" and one.grid == one.cluster == 1
+    three = generate(program, inplace_outputs=inplace, max_blocks=3)
+    assert three.grid == three.cluster == 2                                        # cluster sizes are powers of two
+    # enough work to fill the GPU: barrier through global memory, all SMs
+    big, big_inplace = _step_program("c4")
+    g4 = generate(big, inplace_outputs=big_inplace)
+    assert g4.barrier == "grid" and g4.grid == 148
+    assert generate(big, inplace_outputs=big_inplace, cluster_barrier=True).grid == 8
+    # a kernel that exchanges with peers keeps the grid barrier (its flags are raised after grid barriers)
+    from trainkernel_b200.passes import insert_gradient_exchange
+    assert generate(insert_gradient_exchange(program, 4), inplace_outputs=inplace, world=2).barrier == "grid"

@@ -77,6 +77,7 @@ class GeneratedKernel:
     param_bytes: int = 0
     workspace_bytes: int = 0
     cluster: int = 1                      # thread-block cluster size the kernel must be launched with
+    barrier: str = "grid"                 # "grid": barrier through global memory; "cluster": the grid is one cluster, hardware barrier
     world: int = 1                        # ranks the kernel exchanges with (1: no exchange stages)
     multicast: bool = False               # exchanges through the multicast mapping (one more extra input)
     symmetric_bytes: int = 0              # size of the peer-mapped buffer the kernel expects after the program inputs
@@ -653,7 +654,7 @@ class _Emitter:
         body.depth = 1
         for stage in range(plan.stages):
             if stage:
-                body.emit("tk::grid_barrier(c);")
+                body.emit("tk::cluster_barrier(c);" if plan.cluster_blocks else "tk::grid_barrier(c);")
                 if stage - 1 in plan.signal_barriers:
                     body.emit(f"if (blockIdx.x == 0 && threadIdx.x == 0) tk::dp_signal(c.dp, &P.in[{len(plan.program.inputs) + 1}], {plan.world}, {stage - 1});")
                 if stage_stamps:
@@ -800,7 +801,7 @@ def _check_broadcasts(program: Program) -> None:
 def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = None, fuse_pointwise: bool = True,
                  fuse_epilogues: bool = True, max_blocks: int | None = None, tensor_cores: bool = True,
                  block_n: int | None = None, two_cta: bool | None = None, world: int = 1,
-                 background: bool = False, multicast: bool = False) -> Plan:
+                 background: bool = False, multicast: bool = False, cluster_barrier: bool | None = None) -> Plan:
     """Validate, canonicalise and plan `program` (no code is emitted)."""
     validate(program)
     from .passes import canonicalize_transposed_mm
@@ -829,7 +830,7 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
             raise ValueError("trainkernel: inplace outputs must be computed values, not input views")
     return Planner(program, inplace_outputs=mapping, fuse_pointwise=fuse_pointwise, fuse_epilogues=fuse_epilogues,
                    max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n, two_cta=two_cta, world=world,
-                   background=background, multicast=multicast).plan()
+                   background=background, multicast=multicast, cluster_barrier=cluster_barrier).plan()
 
 
 _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shared_skew", "split_k_gemv",
@@ -840,7 +841,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              max_blocks: int | None = None, inplace_outputs: dict[int, int] | None = None,
              tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
              two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
-             multicast: bool = False, **reference_knobs) -> GeneratedKernel:
+             multicast: bool = False, cluster_barrier: bool | None = None, **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -852,6 +853,10 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     pointwise and exchange units while they wait for the tensor pipe (and places weight-shadow
     casts next to the GEMM before their first use).  Measured on B200 it did not pay off — one warp
     per piece keeps too few loads in flight and delays the epilogues — so it is off by default.
+
+    `cluster_barrier` (default: decided from the amount of work) runs the whole kernel as ONE
+    thread-block cluster of at most 8 blocks whose stages end in the hardware cluster barrier instead
+    of the barrier through global memory; `GeneratedKernel.barrier` says which one a kernel uses.
 
     With `world > 1` the kernel takes `1 + world` extra inputs after the program's own: this rank's
     symmetric buffer, then every rank's mapping of it in rank order.  `multicast=True` adds one more,
@@ -868,7 +873,8 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         raise ValueError("trainkernel: blocks_per_sm must be between 1 and 8")
     plan = plan_program(program, inplace_outputs=inplace_outputs, fuse_pointwise=fuse_pointwise,
                         fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n,
-                        two_cta=two_cta, world=world, background=background, multicast=multicast)
+                        two_cta=two_cta, world=world, background=background, multicast=multicast,
+                        cluster_barrier=cluster_barrier)
     emitter = _Emitter(plan)
     if raster_group is not None:
         if type(raster_group) is not int or not 1 <= raster_group <= 64:
@@ -910,7 +916,8 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         staged_state_commits=len(plan.staged_commits),
         param_bytes=param_bytes,
         workspace_bytes=plan.workspace_bytes,
-        cluster=2 if plan.two_cta else 1,
+        cluster=2 if plan.two_cta else max(1, plan.cluster_blocks),
+        barrier="cluster" if plan.cluster_blocks else "grid",
         world=plan.world,
         multicast=plan.multicast,
         symmetric_bytes=plan.symmetric_bytes,

@@ -254,6 +254,18 @@ __device__ __forceinline__ void grid_barrier(Ctx& c) {
     ++c.stage_id;
 }
 
+// Stage boundary of a kernel whose whole grid is ONE thread-block cluster: the hardware cluster
+// barrier with release / acquire semantics at cluster scope (covers global memory), a fraction of
+// the cost of a barrier through global memory.  It cannot time out, and it does not need to: every
+// thread of every block reaches it, aborted or not, because an aborted block only skips work.
+__device__ __forceinline__ void cluster_barrier(Ctx& c) {
+    fence_proxy_async();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    fence_proxy_async();
+    ++c.stage_id;
+}
+
 // ----------------------------------------------------------------------------
 // rounding helpers: every IR value is rounded to its declared dtype
 // ----------------------------------------------------------------------------

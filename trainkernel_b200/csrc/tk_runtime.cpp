@@ -280,7 +280,7 @@ int tk_module_max_coresident_blocks(tk_module* m, int* out) {
 }
 
 int tk_module_set_cluster(tk_module* m, int size) {
-    if (!m || (size != 1 && size != 2)) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_set_cluster");
+    if (!m || (size != 1 && size != 2 && size != 4 && size != 8)) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_set_cluster");
     if (size == 1) {
         m->cluster = 1;
         m->max_blocks = m->sm_count * m->blocks_per_sm;

@@ -30,6 +30,8 @@ EXCHANGE = frozenset({"allreduce"})
 SYM_HEADER = 4096                      # flag words at the start of the symmetric buffer
 ELEMENT_BYTES = {"float32": 4, "float16": 2, "bfloat16": 2, "int64": 8, "int32": 4, "bool": 1}
 SM_COUNT = 148
+MAX_CLUSTER = 8                         # portable thread-block cluster size
+CLUSTER_WORK_LIMIT = 100_000_000        # flops-equivalents below which a program runs as one cluster
 THREADS = 192
 ALIGN = 256
 
@@ -177,14 +179,16 @@ class Plan:
     signal_barriers: tuple = ()            # grid barriers after which this rank raises its flag at every peer
     background: bool = False               # run memory-bound units inside the epilogue warps of tensor-core stages
     multicast: bool = False                # exchange through the NVSwitch multicast mapping (multimem) instead of scattering
+    cluster_blocks: int = 0                # > 0: the whole grid is ONE thread-block cluster of this many blocks, stages end in the hardware cluster barrier
 
 
 class Planner:
     def __init__(self, program: Program, *, inplace_outputs: dict[int, int] | None = None,
                  fuse_pointwise: bool = True, fuse_epilogues: bool = True, max_blocks: int | None = None,
                  tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None, world: int = 1, background: bool = False,
-                 multicast: bool = False):
+                 multicast: bool = False, cluster_barrier: bool | None = None):
         self.program = program
+        self.cluster_barrier = cluster_barrier
         self.inplace = dict(inplace_outputs or {})
         self.fuse_pointwise = fuse_pointwise
         self.fuse_epilogues = fuse_epilogues
@@ -749,9 +753,22 @@ class Planner:
             grid = max(1, min(grid, self.max_blocks))
         if two_cta:
             grid = max(2, grid - grid % 2)
+        # Small programs are bound by the latency of their stage boundaries, not by throughput: run them as
+        # ONE cluster of at most 8 blocks, whose hardware barrier costs a fraction of a barrier through global
+        # memory, instead of spreading a few microseconds of work over the whole GPU.
+        work = 0
+        for unit in units:
+            work += 2 * prod(unit.mnk) if unit.kind == "gemm" else 16 * max(1, prod(unit.dims)) * (max(1, prod(unit.reduced)) if unit.kind == "reduce" else 1)
+        small = self.world == 1 and not two_cta and work <= CLUSTER_WORK_LIMIT
+        cluster_blocks = 0
+        if small if self.cluster_barrier is None else (self.cluster_barrier and self.world == 1 and not two_cta):
+            cluster_blocks = 1
+            while cluster_blocks * 2 <= min(MAX_CLUSTER, grid):
+                cluster_blocks *= 2
+            grid = cluster_blocks
         return Plan(program, sorted(units, key=lambda u: (u.stage, u.index)), stage_count, storage, dtypes, shapes,
                     max(total, ALIGN), inlined, direct, staged, native, grid, tc_units, tc_units > 0, two_cta,
-                    self.world, symmetric if symmetric > SYM_HEADER else 0, tuple(sorted(signal)), self.background, self.multicast)
+                    self.world, symmetric if symmetric > SYM_HEADER else 0, tuple(sorted(signal)), self.background, self.multicast, cluster_blocks)
 
     # -- helpers ---------------------------------------------------------------------
     def _refs(self, expr) -> set[str]:

@@ -182,6 +182,9 @@ class _Module:
         self.grid = max(1, min(generated.grid, limit.value))
         if generated.cluster > 1:
             self.grid -= self.grid % generated.cluster
+        if generated.barrier == "cluster" and self.grid != generated.cluster:
+            raise RuntimeError(f"trainkernel: a kernel synchronised by the cluster barrier must run as one cluster of "
+                               f"{generated.cluster} blocks; the device admits {limit.value}")
         self.n_in = max(1, generated.input_count)
         self.n_out = max(1, generated.output_count)
 
