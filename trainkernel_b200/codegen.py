@@ -115,6 +115,7 @@ class _Emitter:
         self.functors: list[str] = []
         self.needs_simt = False
         self.raster_group = 8
+        self.trace_stage = None
         self.rows = False
         self.background = plan.background
 
@@ -385,7 +386,7 @@ class _Emitter:
         elif unit.path == "gemv":
             k_major = b.strides[0] == 1 and b.strides[1] != 1
             ld = b.strides[1] if k_major else b.strides[0]
-            body.emit(f"tk::gemv<{CTYPE[a.dtype]}, {ROUND[a.round_to]}, {CTYPE[b.dtype]}, {ROUND[b.round_to]}, {str(k_major).lower()}, {epi}>(c, P, "
+            body.emit(f"tk::gemv<{CTYPE[a.dtype]}, {ROUND[a.round_to]}, {CTYPE[b.dtype]}, {ROUND[b.round_to]}, {str(k_major).lower()}, {unit.block_n or 64}, {epi}>(c, P, "
                       f"{self.pointer(a.buffer, a.dtype, True)} + {a.offset}LL, {a.strides[1]}LL, "
                       f"{self.pointer(b.buffer, b.dtype, True)} + {b.offset}LL, {ld}LL, {n}, {k}, {base}LL);")
         else:
@@ -731,7 +732,9 @@ class _Emitter:
         n_maps = max(1, len(self.maps))
         n_maps_used = len(self.maps)
         use_tc = "true" if plan.uses_tc else "false"
-        header = [
+        widest = max((u.block_n for u in plan.units if u.kind == "gemm" and u.path == "tc"), default=256)
+        ring = ([] if plan.two_cta else [f"#define TK_RING_BN {64 if widest <= 64 else 128 if widest <= 128 else 256}"])
+        header = ring + ([f"#define TK_TRACE_STAGE {int(self.trace_stage)}"] if self.trace_stage is not None else []) + [
             '#include "tk_gemm_2cta.cuh"' if plan.two_cta else '#include "tk_device.cuh"',
             "struct Params {",
             f"    CUtensorMap maps[{n_maps}];",
@@ -841,7 +844,8 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              max_blocks: int | None = None, inplace_outputs: dict[int, int] | None = None,
              tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
              two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
-             multicast: bool = False, cluster_barrier: bool | None = None, **reference_knobs) -> GeneratedKernel:
+             multicast: bool = False, cluster_barrier: bool | None = None, trace_stage: int | None = None,
+             **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -857,6 +861,10 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     `cluster_barrier` (default: decided from the amount of work) runs the whole kernel as ONE
     thread-block cluster of at most 8 blocks whose stages end in the hardware cluster barrier instead
     of the barrier through global memory; `GeneratedKernel.barrier` says which one a kernel uses.
+
+    `trace_stage=s` (with `stage_stamps=True`) also records six role-level timestamps of the first
+    single-CTA tensor-core tile of stage `s` in stamp slots 32..37 (`CompiledProgram.stage_stamps`
+    returns them after the per-stage values when asked for 38 entries).
 
     With `world > 1` the kernel takes `1 + world` extra inputs after the program's own: this rank's
     symmetric buffer, then every rank's mapping of it in rank order.  `multicast=True` adds one more,
@@ -876,6 +884,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
                         two_cta=two_cta, world=world, background=background, multicast=multicast,
                         cluster_barrier=cluster_barrier)
     emitter = _Emitter(plan)
+    emitter.trace_stage = trace_stage
     if raster_group is not None:
         if type(raster_group) is not int or not 1 <= raster_group <= 64:
             raise ValueError("trainkernel: raster_group must be between 1 and 64")

@@ -24,15 +24,24 @@ constexpr int kEpiThreads = 128;
 constexpr int BM = 128;                // UMMA M
 constexpr int BK = 64;                 // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kStages = 4;            // cta_group::1 ring: 4 x 48 KiB
+// The widest N tile any cta_group::1 GEMM of this kernel uses (a generated kernel defines it before
+// including this file).  Narrower tiles take less room per K block, and the room goes into a deeper
+// ring: a small GEMM is bound by the latency of its operand loads, so bytes in flight are what count.
+#ifndef TK_RING_BN
+#define TK_RING_BN 256
+#endif
+constexpr int kRingBN = TK_RING_BN;
+static_assert(kRingBN == 64 || kRingBN == 128 || kRingBN == 256, "TK_RING_BN must be 64, 128 or 256");
+constexpr int kStages = kRingBN == 256 ? 4 : (kRingBN == 128 ? 6 : 8);   // cta_group::1 ring: 4 x 48, 6 x 32 or 8 x 24 KiB
 constexpr int kStages2 = 6;           // cta_group::2 ring: 6 x 32 KiB
 constexpr int kMaxStages = 8;
-constexpr int kMaxBN = 256;
+constexpr int kMaxBN = 256;            // accumulator pitch in TMEM columns
 constexpr int kSlotA = BM * BK * 2;    // 16 KiB
-constexpr int kSlotB = kMaxBN * BK * 2;  // 32 KiB
+constexpr int kSlotB = kRingBN * BK * 2;  // 8, 16 or 32 KiB
 constexpr int kSlotBytes = kSlotA + kSlotB;
 constexpr int kTmemCols = 512;         // two 256-column FP32 accumulators
-constexpr int kDynSmem = kStages * kSlotBytes + 1024;  // +1024 for manual alignment
+constexpr int kDynSmem = 4 * (kSlotA + kMaxBN * BK * 2) + 1024;  // 192 KiB for any ring shape, +1024 for manual alignment
+static_assert(kStages * kSlotBytes + 1024 <= kDynSmem && kStages <= kMaxStages, "ring does not fit");
 
 enum : uint32_t {
     kOk = 0,
@@ -827,10 +836,20 @@ __device__ __forceinline__ void epilogue_chunk(Ctx& c, const Params& P, const fl
 // {64 (MN), 64 (K)} box issued once per 64-wide MN atom.  Out-of-range parts of a box are
 // zero-filled by TMA, which is what makes M, N and K tails work.
 // ----------------------------------------------------------------------------
+// Optional role-level timestamps of ONE stage's first tensor-core tile (compile with
+// -DTK_TRACE_STAGE=<stage>): the thread that reaches point k while working on tile 0 of that stage
+// writes the global timer to stamp slot 32 + k.  Points: 0 producer starts, 1 last TMA issued,
+// 2 first operands landed, 3 last MMA committed, 4 accumulator seen complete, 5 epilogue done.
+#ifdef TK_TRACE_STAGE
+#define TK_TRACE(point, tile) do { if (c.stage_id == TK_TRACE_STAGE && (tile) == 0) P.stamps[32 + (point)] = global_timer_ns(); } while (0)
+#else
+#define TK_TRACE(point, tile) do { } while (0)
+#endif
+
 template <int BN, bool A_MN, bool B_MN, int FMT, typename Epi, typename Bg, typename Params>
 __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorMap* map_a, const CUtensorMap* map_b,
                                         int M, int N, int K, int64_t item_base) {
-    static_assert(BN % 64 == 0 && BN <= kMaxBN, "BN must be 64, 128, 192 or 256");
+    static_assert(BN % 64 == 0 && BN <= kRingBN, "BN must be a multiple of 64 within the ring's tile width");
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
     const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n;
     const int kblocks = (K + BK - 1) / BK;
@@ -842,6 +861,7 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
         if (c.lane == 0) {
             for (int64_t t = first_item(item_base); t < tiles && !c.aborted(); t += step) {
                 int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+                TK_TRACE(0, t);
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!c.wait(&sh->empty[c.slot], c.slot_phase ^ 1, kErrSmemEmpty)) break;
                     uint8_t* sa = c.slots + c.slot * kSlotBytes;
@@ -861,6 +881,7 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
                     }
                     c.advance_slot();
                 }
+                TK_TRACE(1, t);
             }
         }
         __syncwarp();
@@ -875,6 +896,7 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!c.wait(&sh->full[c.slot], c.slot_phase, kErrSmemFull)) { ok = false; break; }
                     tc_fence_after();
+                    if (kb == 0) TK_TRACE(2, t);
                     const uint32_t sa = smem_u32(c.slots + c.slot * kSlotBytes);
                     const uint32_t sb = sa + kSlotA;
 #pragma unroll
@@ -888,6 +910,7 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
                 }
                 if (!ok) break;
                 tc_commit(&sh->tmem_full[c.acc]);      // accumulator complete
+                TK_TRACE(3, t);
                 c.advance_acc();
             }
         }
@@ -906,6 +929,7 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
             }
             if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
             tc_fence_after();
+            if (threadIdx.x == 64) TK_TRACE(4, t);
             const int row0 = tm * BM + quarter * 32;
             const uint32_t taddr = c.tmem + c.acc * kMaxBN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
@@ -920,6 +944,7 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
             tc_fence_before();
             __syncwarp();
             if (c.lane == 0) mbar_arrive(&sh->tmem_empty[c.acc]);
+            if (threadIdx.x == 64) TK_TRACE(5, t);
             c.advance_acc();
         }
     }
@@ -949,27 +974,30 @@ __device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm,
         for (int k0 = 0; k0 < K; k0 += kSimtK) {
             const int depth = min(kSimtK, K - k0);
             __syncthreads();
-            // Stage A[32, depth] and B[depth, 32]; eight independent loads per thread are issued
-            // before the first shared-memory store so their latencies overlap.
-            for (int p0 = tid; p0 < 32 * depth; p0 += kThreads * 8) {
+            // Stage A[32, depth] and B[depth, 32].  Positions are decomposed against the fixed staging
+            // depth (shifts and masks, no division by a runtime value) and the part beyond `depth` is
+            // skipped; eight independent loads per thread are issued before the first shared-memory
+            // store so their latencies overlap.  Consecutive threads walk the unit-stride axis.
+            for (int p0 = tid; p0 < 32 * kSimtK; p0 += kThreads * 8) {
                 float va[8], vb[8];
                 int ia[8], ib[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const int p = p0 + u * kThreads;
-                    const bool live = p < 32 * depth;
-                    // consecutive threads walk the unit-stride axis of each operand
-                    const int ar = a_k_fast ? p / depth : p % 32, ak = a_k_fast ? p % depth : p / 32;
-                    const int bk = b_n_fast ? p / 32 : p % depth, bc = b_n_fast ? p % 32 : p / depth;
-                    ia[u] = live ? ar * (kSimtK + 1) + ak : -1;
-                    ib[u] = live ? bk * 36 + bc : -1;
+                    const int ar = a_k_fast ? p / kSimtK : p % 32, ak = a_k_fast ? p % kSimtK : p / 32;
+                    const int bk = b_n_fast ? p / 32 : p % kSimtK, bc = b_n_fast ? p % 32 : p / kSimtK;
+                    const bool in_tile = p < 32 * kSimtK;
+                    const bool live_a = in_tile && ak < depth, live_b = in_tile && bk < depth;
+                    ia[u] = live_a ? ar * (kSimtK + 1) + ak : -1;
+                    ib[u] = live_b ? bk * 36 + bc : -1;
                     const int gr = row0 + ar, gc = col0 + bc;
-                    va[u] = (live && gr < M) ? RA::rnd(to_f32(A[static_cast<int64_t>(gr) * a_rs + static_cast<int64_t>(k0 + ak) * a_ks])) : 0.0f;
-                    vb[u] = (live && gc < N) ? RB::rnd(to_f32(B[static_cast<int64_t>(k0 + bk) * b_ks + static_cast<int64_t>(gc) * b_cs])) : 0.0f;
+                    va[u] = (live_a && gr < M) ? RA::rnd(to_f32(A[static_cast<int64_t>(gr) * a_rs + static_cast<int64_t>(k0 + ak) * a_ks])) : 0.0f;
+                    vb[u] = (live_b && gc < N) ? RB::rnd(to_f32(B[static_cast<int64_t>(k0 + bk) * b_ks + static_cast<int64_t>(gc) * b_cs])) : 0.0f;
                 }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    if (ia[u] >= 0) { (&sm->a[0][0])[ia[u]] = va[u]; (&sm->b[0][0])[ib[u]] = vb[u]; }
+                    if (ia[u] >= 0) (&sm->a[0][0])[ia[u]] = va[u];
+                    if (ib[u] >= 0) (&sm->b[0][0])[ib[u]] = vb[u];
                 }
             }
             __syncthreads();
@@ -1004,7 +1032,7 @@ __device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm,
 //   otherwise B has unit stride along N: lane%8 owns 8 consecutive columns, lane/8 strides K
 //             by 4; partial sums of the 4 K groups are combined with two shuffles.
 // ----------------------------------------------------------------------------
-template <typename TA, typename RA, typename TB, typename RB, bool B_KMAJOR, typename Epi, typename Params>
+template <typename TA, typename RA, typename TB, typename RB, bool B_KMAJOR, int CW, typename Epi, typename Params>
 __device__ __forceinline__ void gemv(Ctx& c, const Params& P, const TA* a, int64_t a_ks, const TB* B, int64_t b_ld,
                                      int N, int K, int64_t item_base) {
     constexpr int kWarps = kThreads / 32;
@@ -1029,13 +1057,19 @@ __device__ __forceinline__ void gemv(Ctx& c, const Params& P, const TA* a, int64
             if (n < N && c.lane == 0) Epi::template run<1>(P, 0, n, 1, &acc);
         }
     } else {
-        const int64_t items = (N + 64 * kWarps - 1) / (64 * kWarps);
+        // A warp covers CW columns (64: eight lanes side by side, four K groups; 8: one lane per row
+        // piece, 32 K groups -- the latency-friendly shape for a small matrix, which then spreads over
+        // eight times as many warps with an eighth of the loads per lane).
+        static_assert(CW == 64 || CW == 8, "columns per warp");
+        constexpr int kLanesPerRow = CW / 8, kGroups = 32 / kLanesPerRow;
+        const int64_t items = (N + CW * kWarps - 1) / (CW * kWarps);
         for (int64_t it = first_item(item_base); it < items; it += gridDim.x) {
-            const int n0 = (static_cast<int>(it) * kWarps + c.warp) * 64 + (c.lane & 7) * 8;
+            const int n0 = (static_cast<int>(it) * kWarps + c.warp) * CW + (c.lane % kLanesPerRow) * 8;
             float acc[8] = {};
             if (n0 < N) {
                 const int nvalid = min(8, N - n0);
-                for (int k = c.lane >> 3; k < K; k += 4) {
+#pragma unroll 4
+                for (int k = c.lane / kLanesPerRow; k < K; k += kGroups) {
                     float b[8];
                     ld_row<8>(B + static_cast<int64_t>(k) * b_ld + n0, nvalid, b);
                     const float av = RA::rnd(to_f32(a[static_cast<int64_t>(k) * a_ks]));
@@ -1045,10 +1079,10 @@ __device__ __forceinline__ void gemv(Ctx& c, const Params& P, const TA* a, int64
             }
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 8);
-                acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
+#pragma unroll
+                for (int o = kLanesPerRow; o < 32; o <<= 1) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
             }
-            if (n0 < N && c.lane < 8) Epi::template run<8>(P, 0, n0, min(8, N - n0), acc);
+            if (n0 < N && c.lane < kLanesPerRow) Epi::template run<8>(P, 0, n0, min(8, N - n0), acc);
         }
     }
 }

@@ -758,7 +758,10 @@ class Planner:
         # memory, instead of spreading a few microseconds of work over the whole GPU.
         work = 0
         for unit in units:
-            work += 2 * prod(unit.mnk) if unit.kind == "gemm" else 16 * max(1, prod(unit.dims)) * (max(1, prod(unit.reduced)) if unit.kind == "reduce" else 1)
+            if unit.kind == "gemm":
+                work += 2 * prod(unit.mnk) * (1 if unit.path in ("tc", "tc2") else 16)      # CUDA-core products want more SMs
+            else:
+                work += 16 * max(1, prod(unit.dims)) * (max(1, prod(unit.reduced)) if unit.kind == "reduce" else 1)
         small = self.world == 1 and not two_cta and work <= CLUSTER_WORK_LIMIT
         cluster_blocks = 0
         if small if self.cluster_barrier is None else (self.cluster_barrier and self.world == 1 and not two_cta):
@@ -868,7 +871,7 @@ class Planner:
             if wide:
                 unit_strides = [d for d, s in enumerate(wide[0].strides) if s == 1]
                 inner_kept = bool(unit_strides) and unit_strides[-1] < kept_rank
-            if outputs >= 32 and (inner_kept or size <= 128):
+            if (outputs >= 32 and (inner_kept or size <= 128)) or size <= 32:      # a few terms per output: one thread each
                 unit.strategy = "thread"
                 unit.vector = bool(unit.kept[-1] % 8 == 0 and outputs >= 8 * THREADS and loads
                                    and all(a.strides[kept_rank - 1] in (0, 1) for a in loads))
@@ -910,7 +913,13 @@ class Planner:
                 unit.block_n = choice
                 unit.items = tiles_m * -(-n // choice)
             elif unit.path == "gemv":
-                per = 6 if unit.b.strides[0] == 1 and unit.b.strides[1] != 1 else 6 * 64
+                warps = THREADS // 32
+                if unit.b.strides[0] == 1 and unit.b.strides[1] != 1:
+                    per = warps                              # K-major weight: one warp per output column
+                else:
+                    # columns per warp: 64, or 8 when that is what it takes to occupy a handful of blocks
+                    unit.block_n = 64 if -(-n // (64 * warps)) >= MAX_CLUSTER else 8
+                    per = unit.block_n * warps
                 unit.items = -(-n // per)
             else:
                 unit.items = -(-m // 32) * -(-n // 32)

@@ -240,9 +240,9 @@ class CompiledProgram:
             _raise(code)
         return tuple(int(w) for w in words)
 
-    def stage_stamps(self) -> list[int]:
+    def stage_stamps(self, count: int | None = None) -> list[int]:
         """Per-stage %globaltimer values of the last launch (kernel generated with `stage_stamps=True`)."""
-        count = self.generated.stages + 1
+        count = self.generated.stages + 1 if count is None else count
         stamps = (ctypes.c_uint64 * count)()
         stream = torch.cuda.current_stream(self.device).cuda_stream
         code = self.module.lib.tk_module_stage_stamps(self.module.handle, stream, stamps, count)
