@@ -227,6 +227,7 @@ def small_config_latencies() -> dict:
         bound_us = max(work.flops_per_step() / (_peaks()["tflops"] * 1e12), work.bytes_per_step() / (_peaks()["hbm_gbs"] * 1e9)) * 1e6
         result[work.name] = {"latency_us_p50": round(p50, 2), "steps_per_s": round(1e6 / p50, 1),
                              "grid_barriers": compiled.runner.generated.grid_barriers,
+                             "barrier": compiled.runner.generated.barrier, "blocks": compiled.runner.module.grid,
                              "roofline_us": round(bound_us, 3), "roofline_frac": round(bound_us / p50, 4)}
     return result
 

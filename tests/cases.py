@@ -142,6 +142,15 @@ CASES = {
     "mlp_2cta": mlp_case((512, 1024, 768, 512), 512, two_cta=True),
     "mlp_1cta": mlp_case((512, 1024, 768, 512), 512, two_cta=False),
     "mlp_2cta_background": mlp_case((512, 1024, 768, 512), 512, two_cta=True, background=True),
+    # fusion boundaries (reference: tests/test_epilogues_gpu.py, tests/test_side_epilogues.py)
+    "observable_product": function_case(lambda a, b: (a @ b, torch.relu(a @ b) + 1.0), [(40, 24), (24, 56)]),
+    "transposed_operand_broadcast_chain": function_case(lambda a, b, row, col: torch.relu(a.t() @ b + row) * col, [(24, 40), (24, 56), (56,), (40, 1)]),
+    "rounding_boundary_bf16": function_case(lambda a, b, c: (((a @ b).float() * 3.0 + c.float()).to(BF16), (a @ b).float().sum()),
+                                            [(136, 72), (72, 200), (136, 200)], BF16),
+    "branched_outputs_one_product": function_case(lambda a, b: (torch.relu(a @ b), (a @ b) * 2.0, ((a @ b) + 1.0).t()), [(48, 32), (32, 48)]),
+    "huge_reduction": function_case(lambda x: ((x + 0.5).sum(), (x + 0.5).mean(), x.sum(0), x.mean(1)), [(2048, 1031)]),
+    "huge_reduction_bf16": function_case(lambda x: ((x.float() + 0.5).sum(), x.sum(0)), [(2048, 1031)], BF16),
+    "original_and_update": function_case(lambda x: (x, x + 1.0), [(8192,)], inplace_outputs={1: 0}),
     # general subset
     "addmm_scaled": function_case(lambda c, a, b: torch.relu(torch.addmm(c, a, b, beta=0.5, alpha=-1.5)), [(40,), (24, 56), (56, 40)]),
     "addmm_scaled_bf16": function_case(lambda c, a, b: torch.addmm(c, a, b, beta=2.0, alpha=0.25), [(136, 72), (136, 200), (200, 72)], BF16),

@@ -976,28 +976,29 @@ __device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm,
             __syncthreads();
             // Stage A[32, depth] and B[depth, 32].  Positions are decomposed against the fixed staging
             // depth (shifts and masks, no division by a runtime value) and the part beyond `depth` is
-            // skipped; eight independent loads per thread are issued before the first shared-memory
-            // store so their latencies overlap.  Consecutive threads walk the unit-stride axis.
-            for (int p0 = tid; p0 < 32 * kSimtK; p0 += kThreads * 8) {
-                float va[8], vb[8];
-                int ia[8], ib[8];
+            // skipped.  A thread issues ALL of its loads of the step (22 per operand) before its first
+            // shared-memory store: one round trip to memory per step.  Consecutive threads walk the
+            // unit-stride axis of each operand.
+            constexpr int kPerThread = (32 * kSimtK + kThreads - 1) / kThreads;
+            float va[kPerThread], vb[kPerThread];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int p = p0 + u * kThreads;
-                    const int ar = a_k_fast ? p / kSimtK : p % 32, ak = a_k_fast ? p % kSimtK : p / 32;
-                    const int bk = b_n_fast ? p / 32 : p % kSimtK, bc = b_n_fast ? p % 32 : p / kSimtK;
-                    const bool in_tile = p < 32 * kSimtK;
-                    const bool live_a = in_tile && ak < depth, live_b = in_tile && bk < depth;
-                    ia[u] = live_a ? ar * (kSimtK + 1) + ak : -1;
-                    ib[u] = live_b ? bk * 36 + bc : -1;
-                    const int gr = row0 + ar, gc = col0 + bc;
-                    va[u] = (live_a && gr < M) ? RA::rnd(to_f32(A[static_cast<int64_t>(gr) * a_rs + static_cast<int64_t>(k0 + ak) * a_ks])) : 0.0f;
-                    vb[u] = (live_b && gc < N) ? RB::rnd(to_f32(B[static_cast<int64_t>(k0 + bk) * b_ks + static_cast<int64_t>(gc) * b_cs])) : 0.0f;
-                }
+            for (int u = 0; u < kPerThread; ++u) {
+                const int p = tid + u * kThreads;
+                const int ar = a_k_fast ? p / kSimtK : p % 32, ak = a_k_fast ? p % kSimtK : p / 32;
+                const int bk = b_n_fast ? p / 32 : p % kSimtK, bc = b_n_fast ? p % 32 : p / kSimtK;
+                const bool in_tile = p < 32 * kSimtK;
+                const int gr = row0 + ar, gc = col0 + bc;
+                va[u] = (in_tile && ak < depth && gr < M) ? RA::rnd(to_f32(A[static_cast<int64_t>(gr) * a_rs + static_cast<int64_t>(k0 + ak) * a_ks])) : 0.0f;
+                vb[u] = (in_tile && bk < depth && gc < N) ? RB::rnd(to_f32(B[static_cast<int64_t>(k0 + bk) * b_ks + static_cast<int64_t>(gc) * b_cs])) : 0.0f;
+            }
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    if (ia[u] >= 0) (&sm->a[0][0])[ia[u]] = va[u];
-                    if (ib[u] >= 0) (&sm->b[0][0])[ib[u]] = vb[u];
+            for (int u = 0; u < kPerThread; ++u) {
+                const int p = tid + u * kThreads;
+                const int ar = a_k_fast ? p / kSimtK : p % 32, ak = a_k_fast ? p % kSimtK : p / 32;
+                const int bk = b_n_fast ? p / 32 : p % kSimtK, bc = b_n_fast ? p % 32 : p / kSimtK;
+                if (p < 32 * kSimtK) {
+                    if (ak < depth) sm->a[ar][ak] = va[u];
+                    if (bk < depth) sm->b[bk][bc] = vb[u];
                 }
             }
             __syncthreads();
