@@ -58,6 +58,8 @@ def main(argv=None) -> int:
     parser.add_argument("--repeats", type=int, default=10)
     parser.add_argument("--plain", action="store_true")
     parser.add_argument("--device", default="cuda:0")
+    parser.add_argument("--trace-stage", type=int, default=None,
+                        help="also time the roles of the first single-CTA tensor-core tile of this stage")
     args = parser.parse_args(argv)
     work = workloads.build(args.workload, device=args.device)
     inputs = (work.state, *work.batches[0])
@@ -68,6 +70,20 @@ def main(argv=None) -> int:
         torch.cuda.synchronize()
         compiled.runner.status()
         print(json.dumps({"workload": work.name, "launches": args.repeats, "stages": compiled.runner.generated.stages}))
+        return 0
+    if args.trace_stage is not None:
+        compiled = compile_training(work.fn(), inputs, stage_stamps=True, trace_stage=args.trace_stage)
+        best = None
+        for _ in range(3 + args.repeats):
+            compiled(*inputs)
+            stamps = compiled.runner.stage_stamps(38)
+            start = stamps[args.trace_stage]
+            points = [(value - start) / 1e3 for value in stamps[32:38]] + [(stamps[args.trace_stage + 1] - start) / 1e3]
+            if best is None or points[-1] < best[-1]:
+                best = points
+        names = ("producer_starts", "last_tma_issued", "first_operands_landed", "last_mma_committed",
+                 "accumulator_complete", "epilogue_done", "stage_ends")
+        print(json.dumps({"workload": work.name, "stage": args.trace_stage, "us_after_stage_start": dict(zip(names, best))}))
         return 0
     records = stage_profile(work.fn(), inputs, repeats=args.repeats)
     for record in records:
