@@ -220,6 +220,9 @@ class CompiledProgram:
         self.module = module
         self.device = device
         self.inplace_outputs = dict(inplace_outputs or {})
+        # what every call compares its arguments with, looked up once
+        self._input_meta = [(spec.shape, spec.strides, getattr(torch, spec.dtype)) for spec in program.inputs]
+        self._output_meta = [(spec.shape, getattr(torch, spec.dtype)) for spec in program.outputs]
 
     # -- introspection -------------------------------------------------------------
     def resource_usage(self) -> dict[str, int]:
@@ -252,16 +255,16 @@ class CompiledProgram:
 
     # -- argument checks -------------------------------------------------------------
     def _validate_inputs(self, inputs: tuple[torch.Tensor, ...]) -> None:
-        expected = self.program.inputs
+        expected = self._input_meta
         if len(inputs) != len(expected):
             raise ValueError(f"trainkernel: expected {len(expected)} inputs, got {len(inputs)}")
-        for position, (tensor, spec) in enumerate(zip(inputs, expected)):
+        for position, (tensor, (shape, strides, dtype)) in enumerate(zip(inputs, expected)):
             if not isinstance(tensor, torch.Tensor):
                 raise TypeError(f"trainkernel: input {position} must be a tensor")
             if tensor.is_neg() or tensor.is_conj():
                 raise ValueError("trainkernel: resolve lazy negative or conjugate input views before execution")
-            same = (tensor.device == self.device and tuple(tensor.shape) == spec.shape
-                    and tuple(tensor.stride()) == spec.strides and tensor.dtype == getattr(torch, spec.dtype))
+            same = (tensor.dtype == dtype and tensor.shape == shape and tensor.stride() == strides
+                    and tensor.device == self.device)
             if not same:
                 raise ValueError(f"trainkernel: input {position} does not match compiled device, shape, stride, or dtype")
         for target in self.inplace_outputs.values():
@@ -271,12 +274,15 @@ class CompiledProgram:
     def allocate(self, *inputs: torch.Tensor) -> ExecutionBuffers:
         if self.inplace_outputs:
             self._validate_inputs(inputs)
+        return self._fresh_buffers(inputs)
+
+    def _fresh_buffers(self, inputs: tuple[torch.Tensor, ...]) -> ExecutionBuffers:
         outputs = []
-        for slot, spec in enumerate(self.program.outputs):
+        for slot, (shape, dtype) in enumerate(self._output_meta):
             if slot in self.inplace_outputs:
                 outputs.append(inputs[self.inplace_outputs[slot]])
             else:
-                outputs.append(torch.empty(spec.shape, dtype=getattr(torch, spec.dtype), device=self.device))
+                outputs.append(torch.empty(shape, dtype=dtype, device=self.device))
         workspace = torch.empty(self.generated.workspace_elements, dtype=torch.float32, device=self.device)
         return ExecutionBuffers(tuple(outputs), workspace)
 
@@ -326,7 +332,22 @@ class CompiledProgram:
         return buffers.outputs
 
     def __call__(self, *inputs: torch.Tensor) -> tuple[torch.Tensor, ...]:
-        return self.run_into(*inputs, buffers=self.allocate(*inputs))
+        # Buffers made here are new allocations (or the in-place targets themselves), so of the buffer checks
+        # only one can fail: an in-place target that shares storage with another input.
+        self._validate_inputs(inputs)
+        for index in self.inplace_outputs.values():
+            target = inputs[index]
+            if target.numel():
+                storage = target.untyped_storage().data_ptr()
+                for other, value in enumerate(inputs):
+                    if other != index and value.numel() and value.untyped_storage().data_ptr() == storage:
+                        raise ValueError("trainkernel: inplace target must not alias another input")
+        buffers = self._fresh_buffers(inputs)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self.module.launch(inputs, buffers.outputs, buffers.workspace, stream)
+        if self.inplace_outputs:
+            torch.autograd.graph.increment_version([inputs[i] for i in self.inplace_outputs.values()])
+        return buffers.outputs
 
 
 def compile_program(program: Program, example_inputs: tuple[Any, ...] | list[Any], *,
