@@ -306,6 +306,24 @@ def main() -> None:
 
     for i in range(warmup):
         step(state, *work.batches[i % len(work.batches)])
+        if i == 0 and world > 1 and args.dp == "fused" and step.multicast:
+            # The multicast form depends on the fabric accepting multimem accesses from inside this kernel.
+            # Its waits are bounded, so a refusal shows up as an error status, not a hang: if ANY rank
+            # reports one after the first step, every rank rebuilds the step in the peer-store form.
+            torch.cuda.synchronize()
+            failed = torch.zeros(1, dtype=torch.int32, device=device)
+            try:
+                status()
+            except RuntimeError as error:
+                print(f"[bench] rank {rank}: multicast exchange failed on its first step ({error}); using peer stores", file=sys.stderr)
+                failed += 1
+            dist.all_reduce(failed, op=dist.ReduceOp.MAX)
+            if int(failed.item()):
+                work = workloads.mlp_workload(work.name, MEDIUM_SIZES, MEDIUM_BATCH, seed=0, device=device, rows=rows)
+                state = work.state
+                step = dp.FusedShardedTrainingStep(work.fn(), (state, *work.batches[0]), multicast=False)
+                status, generated = step.status, step.generated
+                step(state, *work.batches[0])
     barrier()
     losses = []
     if args.eager:
