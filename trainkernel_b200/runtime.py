@@ -373,7 +373,15 @@ def compile_program(program: Program, example_inputs: tuple[Any, ...] | list[Any
     cubin = build_cubin(generated.source, verbose=verbose)
     with torch.cuda.device(device):
         torch.cuda.current_stream(device)     # make sure the primary context exists before the shim retains it
-        module = _Module(generated, cubin, device)
+        try:
+            module = _Module(generated, cubin, device)
+        except RuntimeError:
+            # A device partition too small to hold the kernel's one cluster: the same program with the
+            # barrier through global memory runs anywhere.  An explicit request for the cluster form stands.
+            if generated.barrier != "cluster" or generated.cluster == 1 or options.get("cluster_barrier"):
+                raise
+            generated = generate(program, inplace_outputs=inplace_outputs, **{**options, "cluster_barrier": False})
+            module = _Module(generated, build_cubin(generated.source, verbose=verbose), device)
     runner = CompiledProgram(program, generated, module, device, inplace_outputs)
     runner._validate_inputs(tuple(flat))
     return runner
