@@ -121,7 +121,7 @@ CASES = {
     "gemm_odd_bf16": gemm_case(17, 65, 33, "k", "mn"),
     "gemv_n": gemm_case(1, 200, 128, "k", "mn"),
     "gemv_k": gemm_case(1, 200, 128, "k", "k"),
-    # BASELINE configurations and the batch-1 pin
+    # the five benchmark configurations (C1..C4 here) and the batch-1 pin
     "c1": workload_case("c1"),
     "c2": workload_case("c2"),
     "c1_grid_barrier": workload_case("c1", cluster_barrier=False),

@@ -79,7 +79,7 @@ def leaves(state):
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="checkout of the unmodified reference project (arpjw/trainkernel)")
     parser.add_argument("--only", default=None)
     args = parser.parse_args()
     sys.path.insert(0, args.reference)

@@ -1,4 +1,4 @@
-"""100-step trajectories and 20-step CUDA-graph replays of the BASELINE configurations.
+"""100-step trajectories and 20-step CUDA-graph replays of the benchmark configurations C1..C4.
 
 Every step's loss, the last step's gradients and the final state are compared
 with the fixtures that the unmodified reference produced

@@ -188,7 +188,7 @@ CONFIG_NAMES = ("c1", "c2", "c3", "c4", "c5", "gemv")
 
 
 def build(name: str, *, seed: int = 0, device: str | torch.device = "cpu", rows: slice | None = None) -> Workload:
-    """The BASELINE configurations by short name, plus the batch-1 GEMV pin."""
+    """The benchmark configurations C1..C5 by short name, plus the batch-1 GEMV pin."""
     if name == "c1":
         return least_squares_workload(seed=seed, device=device)
     if name == "c2":
