@@ -250,6 +250,10 @@ def main() -> None:
     parser.add_argument("--dp", default="fused", choices=["fused", "nccl"],
                         help="N > 1: gradient exchange inside the step kernel over NVLink peer memory (fused), or "
                              "gradient kernel -> NCCL all-reduce -> update kernel (nccl, the measured baseline)")
+    parser.add_argument("--no-cooperative", action="store_true",
+                        help="N = 1: launch the step kernel without the cooperative-launch attribute (its grid already "
+                             "fits the idle device and its waits are bounded); for hardware profilers that cannot "
+                             "replay cooperative cluster launches")
     parser.add_argument("--no-multicast", action="store_true",
                         help="N > 1, fused: never exchange through the NVSwitch multicast mapping (multimem); "
                              "contributions are then scattered to their owners with plain peer stores")
@@ -288,6 +292,8 @@ def main() -> None:
         kernels_per_step = 1
         status = step.runner.status
         generated = step.runner.generated
+        if args.no_cooperative:
+            runtime.library().tk_module_set_cooperative(step.runner.module.handle, 0)
     elif args.dp == "fused":
         step = dp.FusedShardedTrainingStep(work.fn(), (state, x0, t0), multicast=False if args.no_multicast else None)
         kernels_per_step = step.kernels_per_step

@@ -72,6 +72,14 @@ int tk_module_resource_usage(tk_module* module, int64_t out[4]);
  * New on this back end: the reference's kernels have no cluster dimension (trainkernel/codegen.py:886). */
 int tk_module_set_cluster(tk_module* module, int size);
 
+/* Launch with (1, the default) or without (0) the cooperative-launch attribute.  A kernel that runs as
+ * ONE cluster is co-scheduled by the cluster itself and does not need it.  A grid-barrier kernel
+ * launched without it relies on the grid fitting the idle device (the capacity check of
+ * tk_module_launch still applies, and every wait in the kernel is bounded): meant for hardware
+ * profilers that cannot replay cooperative launches.  No counterpart in the reference, whose launches
+ * are always cooperative (trainkernel/codegen.py:886). */
+int tk_module_set_cooperative(tk_module* module, int enabled);
+
 /* Largest grid a cooperative launch of this kernel accepts on its device. */
 int tk_module_max_coresident_blocks(tk_module* module, int* out);
 

@@ -113,6 +113,7 @@ struct tk_module {
     int sm_count = 0;
     int blocks_per_sm = 0;
     int cluster = 1;
+    std::atomic<int> cooperative{1};
     int max_blocks = 0;               // co-resident capacity for the current cluster size
     size_t param_bytes = 0;
 
@@ -238,11 +239,18 @@ int tk_module_launch(tk_module* m, const void* const* inputs, void* const* outpu
     ContextScope scope(m->context);
     CUlaunchAttribute attribute[2];
     memset(attribute, 0, sizeof(attribute));
-    attribute[0].id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE;
-    attribute[0].value.cooperative = 1;
-    attribute[1].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
-    attribute[1].value.clusterDim.x = static_cast<unsigned>(m->cluster);
-    attribute[1].value.clusterDim.y = attribute[1].value.clusterDim.z = 1;
+    unsigned attributes = 0;
+    if (m->cooperative.load()) {
+        attribute[attributes].id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE;
+        attribute[attributes].value.cooperative = 1;
+        ++attributes;
+    }
+    if (m->cluster > 1) {
+        attribute[attributes].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+        attribute[attributes].value.clusterDim.x = static_cast<unsigned>(m->cluster);
+        attribute[attributes].value.clusterDim.y = attribute[attributes].value.clusterDim.z = 1;
+        ++attributes;
+    }
     CUlaunchConfig config;
     memset(&config, 0, sizeof(config));
     config.gridDimX = static_cast<unsigned>(grid);
@@ -252,7 +260,7 @@ int tk_module_launch(tk_module* m, const void* const* inputs, void* const* outpu
     config.sharedMemBytes = static_cast<unsigned>(m->dynamic_smem);
     config.hStream = static_cast<CUstream>(stream);
     config.attrs = attribute;
-    config.numAttrs = m->cluster > 1 ? 2 : 1;
+    config.numAttrs = attributes;
     void* params[1] = {block};
     if (int rc = check(g_driver.cuLaunchKernelEx_(&config, m->function, params, nullptr), "cuLaunchKernelEx")) return rc;
     g_launches.fetch_add(1);
@@ -306,6 +314,12 @@ int tk_module_set_cluster(tk_module* m, int size) {
     if (clusters < 1) return fail(TK_E_CAPACITY, "trainkernel: no cluster of %d blocks can be resident", size);
     m->cluster = size;
     m->max_blocks = clusters * size;
+    return 0;
+}
+
+int tk_module_set_cooperative(tk_module* m, int enabled) {
+    if (!m) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_set_cooperative");
+    m->cooperative.store(enabled ? 1 : 0);
     return 0;
 }
 

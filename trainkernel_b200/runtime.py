@@ -98,6 +98,7 @@ def library() -> ctypes.CDLL:
         lib.tk_module_set_expected_arrivals.argtypes = [p, u32]
         lib.tk_module_stage_stamps.argtypes = [p, p, ctypes.POINTER(u64), i32]
         lib.tk_module_set_cluster.argtypes = [p, i32]
+        lib.tk_module_set_cooperative.argtypes = [p, i32]
         lib.tk_module_unload.argtypes = [p]
         lib.tk_module_unload.restype = None
         _library = lib
@@ -176,6 +177,8 @@ class _Module:
             code = lib.tk_module_set_cluster(handle, generated.cluster)
             if code:
                 _raise(code)
+        if generated.barrier == "cluster":
+            lib.tk_module_set_cooperative(handle, 0)       # one cluster: co-scheduled by construction
         limit = ctypes.c_int()
         if lib.tk_module_max_coresident_blocks(handle, ctypes.byref(limit)):
             _raise(1)
