@@ -294,6 +294,8 @@ def main() -> None:
         generated = step.runner.generated
         if args.no_cooperative:
             runtime.library().tk_module_set_cooperative(step.runner.module.handle, 0)
+            # should the blocks not all be resident after all, give up on a barrier after 0.2 s instead of 2 s
+            runtime.library().tk_module_set_timeout(step.runner.module.handle, 200_000_000)
     elif args.dp == "fused":
         step = dp.FusedShardedTrainingStep(work.fn(), (state, x0, t0), multicast=False if args.no_multicast else None)
         kernels_per_step = step.kernels_per_step
