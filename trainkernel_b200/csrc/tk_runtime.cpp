@@ -114,6 +114,11 @@ struct tk_module {
     int blocks_per_sm = 0;
     int cluster = 1;
     std::atomic<int> cooperative{1};
+    // Encoded tensor maps of the last launch, keyed by their base address: a caller that launches with the
+    // same buffers again (the common case in an eager loop) does not pay for re-encoding them.
+    std::mutex map_mutex;
+    std::vector<const void*> map_base;
+    std::vector<CUtensorMap> map_cache;
     int max_blocks = 0;               // co-resident capacity for the current cluster size
     size_t param_bytes = 0;
 
@@ -210,15 +215,24 @@ int tk_module_launch(tk_module* m, const void* const* inputs, void* const* outpu
         base += d.byte_offset;
         if (reinterpret_cast<uintptr_t>(base) & 15)
             return fail(TK_E_ARGUMENT, "trainkernel: tensor-core operand %zu is not 16-byte aligned", i);
-        cuuint64_t dims[2] = {d.inner, d.outer};
-        cuuint64_t strides[1] = {d.outer_stride_bytes};
-        cuuint32_t box[2] = {d.box_inner, d.box_outer};
-        cuuint32_t element_strides[2] = {1, 1};
-        CUresult result = g_driver.cuTensorMapEncodeTiled_(
-            reinterpret_cast<CUtensorMap*>(block + 128 * i), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-            const_cast<unsigned char*>(base), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (int rc = check(result, "cuTensorMapEncodeTiled")) return rc;
+        std::lock_guard<std::mutex> guard(m->map_mutex);
+        if (m->map_base.size() != m->maps.size()) {
+            m->map_base.assign(m->maps.size(), nullptr);
+            m->map_cache.resize(m->maps.size());
+        }
+        if (m->map_base[i] != base) {
+            cuuint64_t dims[2] = {d.inner, d.outer};
+            cuuint64_t strides[1] = {d.outer_stride_bytes};
+            cuuint32_t box[2] = {d.box_inner, d.box_outer};
+            cuuint32_t element_strides[2] = {1, 1};
+            CUresult result = g_driver.cuTensorMapEncodeTiled_(
+                &m->map_cache[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                const_cast<unsigned char*>(base), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (int rc = check(result, "cuTensorMapEncodeTiled")) { m->map_base[i] = nullptr; return rc; }
+            m->map_base[i] = base;
+        }
+        memcpy(block + 128 * i, &m->map_cache[i], sizeof(CUtensorMap));
     }
     unsigned char* cursor = block + 128 * static_cast<size_t>(m->slots_maps);
     for (int i = 0; i < m->n_inputs; ++i) memcpy(cursor + 8 * i, &inputs[i], 8);
