@@ -919,6 +919,12 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
         const int quarter = c.warp & 3;                // TMEM lanes this warp may read
         for (int64_t t = first_item(item_base); t < tiles && !c.aborted(); t += step) {
             int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+            if (t == first_item(item_base)) {
+                // the block's first tile of this unit: nobody fetched its epilogue operands yet, and these warps
+                // are idle until the accumulator is complete
+                const int prow = tm * BM + quarter * 32 + c.lane;
+                if (prow < M) Epi::prefetch(P, prow, tn * BN, min(BN, N - tn * BN));
+            }
             if (t + step < tiles) {
                 int pm, pn; tile_coords(t + step, tiles_m, tiles_n, pm, pn);
                 const int prow = pm * BM + quarter * 32 + c.lane;
