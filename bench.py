@@ -35,9 +35,9 @@ if str(ROOT) not in sys.path:
 MEDIUM_SIZES = (4096, 8192, 8192, 8192, 4096)
 MEDIUM_BATCH = 8192
 # DRAM bytes of one medium-MLP step kernel at N = 1 (ncu dram__bytes_read.sum + dram__bytes_write.sum,
-# one-pass capture of the full-size launch of the --single-cta variant, the one ncu is able to launch;
-# see profiles/tk_step_c5_medium_mlp.md).
-MEASURED_TRAFFIC_BYTES = 15.87e9
+# one-pass capture of the full-size launch of the product kernel started with --no-cooperative, the
+# form ncu is able to replay; the summary is in profiles/tk_step_c5_medium_mlp.md).
+MEASURED_TRAFFIC_BYTES = 16.13e9
 
 
 def _peaks() -> dict:
