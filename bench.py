@@ -97,7 +97,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.process = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                                             "--format=csv,noheader,nounits", "-lms", "50"],
+                                             "--format=csv,noheader,nounits", "-lms", "20"],
                                             stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -108,6 +108,19 @@ class ClockSampler:
     def _pump(self):
         for line in self.process.stdout:
             self.lines.append(line.strip())
+
+    def wait_first(self, seconds: float = 3.0) -> None:
+        """Block until nvidia-smi has produced its first line (it takes a few hundred ms to start)."""
+        deadline = time.monotonic() + seconds
+        while self.process is not None and not self.lines and time.monotonic() < deadline:
+            time.sleep(0.01)
+
+    def mark(self) -> None:
+        """Forget the samples taken so far: what follows is the region under load."""
+        del self.lines[:]
+
+    def count(self) -> int:
+        return len(self.lines)
 
     def __exit__(self, *exc):
         if self.process is not None:
@@ -351,6 +364,10 @@ def main() -> None:
     barrier()
     launches_before = runtime.library().tk_launch_count()
     with ClockSampler(local) as sampler:
+        sampler.wait_first()
+        graph.replay()                   # back under load before the samples that count
+        barrier()
+        sampler.mark()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         begin.record()
@@ -368,6 +385,16 @@ def main() -> None:
             b.record()
             barrier()
             samples.append(a.elapsed_time(b) / steps * 1e3)
+        # a short step leaves the 20 ms clock sampler few samples: keep replaying (untimed) until it has a handful
+        extra = 0
+        while world == 1 and sampler.process is not None and sampler.count() < 5 and extra < 50:
+            graph.replay()
+            torch.cuda.synchronize()
+            extra += 1
+        if world > 1:
+            for _ in range(3):           # the same count on every rank: the replays synchronise with each other
+                graph.replay()
+            barrier()
     status()
     clocks = sampler.summary()
     if world > 1:
