@@ -657,7 +657,7 @@ class _Emitter:
             if stage:
                 body.emit("tk::cluster_barrier(c);" if plan.cluster_blocks else "tk::grid_barrier(c);")
                 if stage - 1 in plan.signal_barriers:
-                    body.emit(f"if (blockIdx.x == 0 && threadIdx.x == 0) tk::dp_signal(c.dp, &P.in[{len(plan.program.inputs) + 1}], {plan.world}, {stage - 1});")
+                    body.emit(f"if (blockIdx.x == 0 && threadIdx.x < {plan.world}) tk::dp_signal(c.dp, &P.in[{len(plan.program.inputs) + 1}], threadIdx.x, {stage - 1});")
                 if stage_stamps:
                     body.emit(f"if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[{stage}] = tk::global_timer_ns();")
             body.emit(f"// ---- stage {stage} ----")

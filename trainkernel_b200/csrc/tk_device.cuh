@@ -550,26 +550,26 @@ __device__ __forceinline__ void dp_init(Dp& d, void* symmetric_local) {
     d.epoch = ld_relaxed_gpu(d.flags) + 1u;
     d.rank = ld_relaxed_gpu(d.flags + 1);
 }
-// Called by one thread after grid barrier `barrier`: tell every rank that this rank passed it.
-__device__ __forceinline__ void dp_signal(const Dp& d, const void* const* peers, int world, int barrier) {
-    for (int j = 0; j < world; ++j)
-        st_release_sys(reinterpret_cast<uint32_t*>(const_cast<void*>(peers[j])) + 16 + d.rank * 64 + barrier, d.epoch);
+// Called by threads 0 .. world-1 of ONE block after grid barrier `barrier` (thread j tells rank j that this
+// rank passed it): the release stores, each of which has to wait until this GPU's earlier writes are visible
+// system-wide, then proceed side by side instead of one after the other.
+__device__ __forceinline__ void dp_signal(const Dp& d, const void* const* peers, int peer, int barrier) {
+    st_release_sys(reinterpret_cast<uint32_t*>(const_cast<void*>(peers[peer])) + 16 + d.rank * 64 + barrier, d.epoch);
 }
 // Called by all threads of a block: returns once every rank has passed grid barrier `barrier` of this epoch.
+// Thread j watches rank j's flag, so the (system-scope) polls of the ranks overlap.
 __device__ __forceinline__ void dp_wait(Ctx& c, const Dp& d, int world, int barrier) {
-    if (threadIdx.x == 0 && !c.aborted()) {
-        for (int j = 0; j < world; ++j) {
-            const uint32_t* word = d.flags + 16 + j * 64 + barrier;
-            uint32_t polls = 0;
-            uint64_t start = 0;
-            while (static_cast<int32_t>(ld_acquire_sys(word) - d.epoch) < 0) {
-                if ((++polls & 0x3F) == 0) {
-                    if (start == 0) start = global_timer_ns();
-                    if (c.grid_aborted()) { *reinterpret_cast<volatile uint32_t*>(&c.sh->abort) = 1u; break; }
-                    if (global_timer_ns() - start > c.timeout_ns) { c.fail(kErrPeerFlag, static_cast<uint32_t>(j * 64 + barrier)); break; }
-                }
+    if (threadIdx.x < world && !c.aborted()) {
+        const int j = threadIdx.x;
+        const uint32_t* word = d.flags + 16 + j * 64 + barrier;
+        uint32_t polls = 0;
+        uint64_t start = 0;
+        while (static_cast<int32_t>(ld_acquire_sys(word) - d.epoch) < 0) {
+            if ((++polls & 0x3F) == 0) {
+                if (start == 0) start = global_timer_ns();
+                if (c.grid_aborted() || c.aborted()) { *reinterpret_cast<volatile uint32_t*>(&c.sh->abort) = 1u; break; }
+                if (global_timer_ns() - start > c.timeout_ns) { c.fail(kErrPeerFlag, static_cast<uint32_t>(j * 64 + barrier)); break; }
             }
-            if (c.aborted()) break;
         }
     }
     __syncthreads();
