@@ -110,11 +110,16 @@ def _raise(code: int) -> None:
     raise RuntimeError(message)
 
 
-def build_cubin(source: str, *, verbose: bool = False) -> bytes:
-    """nvcc-compile generated source to an sm_100a cubin; cached by content hash."""
+def cubin_path(source: str) -> Path:
+    """Where the cubin of `source` lives in the cache: keyed by the source, both device headers and the flags."""
     header = (CSRC_DIR / "tk_device.cuh").read_bytes() + (CSRC_DIR / "tk_gemm_2cta.cuh").read_bytes()
     digest = hashlib.sha256(source.encode() + b"\0" + header + b"\0" + " ".join(NVCC_FLAGS).encode()).hexdigest()[:32]
-    cached = CACHE_DIR / f"{digest}.cubin"
+    return CACHE_DIR / f"{digest}.cubin"
+
+
+def build_cubin(source: str, *, verbose: bool = False) -> bytes:
+    """nvcc-compile generated source to an sm_100a cubin; cached by content hash."""
+    cached = cubin_path(source)
     if cached.exists():
         return cached.read_bytes()
     cuda = _cuda_home()
