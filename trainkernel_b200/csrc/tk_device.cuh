@@ -517,12 +517,13 @@ __device__ __forceinline__ void tile_coords(int64_t t, int tiles_m, int tiles_n,
 // Every rank owns one symmetric buffer of identical layout: a 4 KiB header of 32-bit words followed
 // by value regions.  Header: word 0 = number of launches completed (epoch), word 1 = this rank's
 // index, words 16 + 64 * r + k = the epoch in which rank r last passed grid barrier k.  After a grid
-// barrier that peers care about, ONE thread of the rank stores the current epoch into that word of
-// every rank's header with release semantics at system scope; everything the rank wrote before the
-// barrier (to its own or to a peer's memory) is then visible to whoever acquires the word.  Waits
-// are bounded like every other wait in this file.  Peer memory is only ever WRITTEN (plain stores:
-// contributions into the owner's staging area, means into every rank's result region) and never
-// read: no remote loads, no multicast, no TMA on remote memory.
+// barrier that peers care about, threads 0 .. world-1 of one block each store the current epoch into
+// that word of one rank's header with release semantics at system scope; everything the rank wrote
+// before the barrier (to its own or to a peer's memory) is then visible to whoever acquires the
+// word.  Waits are bounded like every other wait in this file.  In the scatter form peer memory is
+// only ever WRITTEN (plain stores: contributions into the owner's staging area, means into every
+// rank's result region); the multicast form reads and writes it through multimem instructions on
+// the NVSwitch multicast mapping.  No TMA and no cluster-multicast load ever touches remote memory.
 // ----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) { uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory"); }
