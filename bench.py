@@ -34,10 +34,20 @@ if str(ROOT) not in sys.path:
 
 MEDIUM_SIZES = (4096, 8192, 8192, 8192, 4096)
 MEDIUM_BATCH = 8192
-# DRAM bytes of one medium-MLP step kernel at N = 1 (ncu dram__bytes_read.sum + dram__bytes_write.sum,
-# one-pass capture of the full-size launch of the product kernel started with --no-cooperative, the
-# form ncu is able to replay; the summary is in profiles/tk_step_c5_medium_mlp.md).
-MEASURED_TRAFFIC_BYTES = 16.13e9
+TRAFFIC_FILE = ROOT / "profiles" / "dram_traffic.json"
+
+
+def measured_traffic(generated) -> float | None:
+    """DRAM bytes per launch of exactly this kernel (ncu dram__bytes_read.sum + dram__bytes_write.sum of a
+    one-pass capture), looked up by the hash of the generated source and device headers; None when the
+    kernel has changed since the capture was taken."""
+    from trainkernel_b200 import runtime
+    try:
+        table = json.loads(TRAFFIC_FILE.read_text())
+    except (OSError, ValueError):
+        return None
+    entry = table.get(runtime.cubin_path(generated.source).stem)
+    return float(entry["bytes"]) if entry else None
 
 
 def _peaks() -> dict:
@@ -153,57 +163,67 @@ def _leaves(state):
     return tuple(state) if isinstance(state, (tuple, list)) else (state,)
 
 
-def cpu_baseline(steps: int, warmup: int) -> dict:
-    """Time the CPU oracle (IR interpreter, a port of the reference's reference.py) on the host cores.
+WORKLOAD_TEXT = "{name} medium MLP {sizes}, global batch {batch}, BF16 compute / FP32 master, SGD lr 1e-3"
 
-    A full medium-MLP step is ~9.4 TFLOP, so two bounded samples of the batch (512 and 1024 rows,
-    full-size weights) are timed and the per-step time is extrapolated linearly in the row count.
+
+def _workload_text(name: str) -> str:
+    return WORKLOAD_TEXT.format(name=name, sizes="-".join(map(str, MEDIUM_SIZES)), batch=MEDIUM_BATCH)
+
+
+def _time_cpu(call, limit: int, budget_s: float) -> list[float]:
+    """Wall-clock seconds of up to `limit` calls, stopping once `budget_s` has been spent (at least one)."""
+    samples, spent = [], 0.0
+    while len(samples) < limit and (not samples or spent + samples[-1] <= budget_s):
+        begin = time.perf_counter()
+        call()
+        samples.append(time.perf_counter() - begin)
+        spent += samples[-1]
+    return samples
+
+
+def cpu_baseline(steps: int = 3, budget_s: float = 25.0) -> dict:
+    """Time FULL medium-MLP steps of the reference's CPU path on the host cores.
+
+    Two forms, both on CPU tensors with every host thread: the IR-interpreter oracle (a port of the
+    reference's reference.py) and eager PyTorch running the step function itself.  Up to `steps`
+    whole steps each (one at least, more while they fit in `budget_s`), after a warm-up on 256 rows
+    that spins the thread pool up; the median is reported.
     """
     import trainkernel_b200 as tk
     from oracle import interpreter
     from trainkernel_b200 import workloads
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    gen = torch.Generator(device="cpu").manual_seed(0)
-    state = []
-    for fan_in, fan_out in zip(MEDIUM_SIZES[:-1], MEDIUM_SIZES[1:]):
-        bound = fan_in ** -0.5
-        state.append((torch.rand((fan_in, fan_out), generator=gen) * 2 - 1) * bound)
-        state.append(torch.zeros(fan_out))
-    timings = {}
-    for rows in (512, 1024):
-        x = torch.randn((rows, MEDIUM_SIZES[0]), generator=gen).to(torch.bfloat16)
-        t = torch.randn((rows, MEDIUM_SIZES[-1]), generator=gen).to(torch.bfloat16)
-        fn = lambda s, xx, tt: workloads.mlp_master_step(s, xx, tt, 1e-3)  # noqa: E731
-        program, _ = tk.capture(fn, (tuple(state), x, t))
-        samples = []
-        for i in range(warmup + steps):
-            begin = time.perf_counter()
-            interpreter.run(program, (*state, x, t))
-            if i >= warmup:
-                samples.append(time.perf_counter() - begin)
-        timings[rows] = statistics.median(samples)
-    slope = (timings[1024] - timings[512]) / 512.0
-    intercept = timings[512] - slope * 512.0
-    full = intercept + slope * MEDIUM_BATCH
-    return {"value": 1.0 / full, "unit": "steps/s", "cores": threads, "kind": "port",
-            "sample": f"IR-interpreter oracle on 512 and 1024 of {MEDIUM_BATCH} batch rows with full-size weights "
-                      f"({timings[512]:.3f} s, {timings[1024]:.3f} s per step), extrapolated linearly in rows to {full:.1f} s per full step",
-            "seconds_per_step_extrapolated": full}
+    work = workloads.mlp_workload("cpu", MEDIUM_SIZES, MEDIUM_BATCH, seed=0, device="cpu", resident=1)
+    x, t = work.batches[0]
+    fn = work.fn()
+    small, _ = tk.capture(fn, (work.state, x[:256], t[:256]))
+    interpreter.run(small, (*work.state, x[:256].contiguous(), t[:256].contiguous()))
+    program, _ = tk.capture(fn, (work.state, x, t))
+    oracle_s = _time_cpu(lambda: interpreter.run(program, (*work.state, x, t)), steps, budget_s)
+    eager_s = _time_cpu(lambda: fn(work.state, x, t), steps, budget_s)
+    per_step = statistics.median(oracle_s)
+    return {"value": 1.0 / per_step, "unit": "steps/s", "cores": threads, "kind": "port",
+            "sample": f"{len(oracle_s)} full step(s) of the IR-interpreter oracle on CPU tensors (all {MEDIUM_BATCH} rows, full-size weights), "
+                      f"median {per_step:.2f} s per step; eager PyTorch on the same tensors: {len(eager_s)} step(s), median {statistics.median(eager_s):.2f} s",
+            "steps_timed": len(oracle_s), "seconds_per_step": per_step,
+            "eager": {"value": 1.0 / statistics.median(eager_s), "unit": "steps/s", "steps_timed": len(eager_s)}}
 
 
 def run_reference(args) -> None:
+    """The reference arm: whole steps of the reference's CPU path, timed on the host cores by rank 0."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
-    base = cpu_baseline(steps, warmup)
+    base = cpu_baseline(max(1, min(args.steps, 3)))
+    timed = base["steps_timed"]
     line = {
         "impl": "reference", "metric": "captured_step_throughput", "value": base["value"], "unit": "steps/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / base["value"],
+        "n_gpus": args.gpus, "steps": timed, "warmup": 1, "ms_per_step": 1e3 / base["value"],
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "c5 medium MLP 4096-8192-8192-8192-4096, global batch 8192, BF16 compute / FP32 master, SGD lr 1e-3",
-                   "timed_steps_per_sample": steps},
+        "config": _config(args.workload, args.gpus, MEDIUM_BATCH // max(1, args.gpus), 4, None, 0),
+        "requested": {"steps": args.steps, "warmup": args.warmup,
+                      "note": "a CPU step takes seconds: at most 3 whole steps are timed after a 256-row warm-up"},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -211,8 +231,61 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
-def small_config_latencies() -> dict:
-    """Graph-replay latency (us per step, p50 of 20 replays of a 20-step graph) of the small configurations."""
+def _config(workload: str, world: int, rows_per_rank: int, resident: int, parallelism: str | None, graph_steps: int) -> dict:
+    """The `config` object, built the same way by both arms so that they describe the same workload."""
+    config = {"workload": _workload_text(workload), "global_batch": MEDIUM_BATCH, "rows_per_rank": rows_per_rank,
+              "resident_batches": resident,
+              "l2": "inputs larger than L2 (FP32 weights %d MB, %d MB per batch)" % (
+                  sum(a * b for a, b in zip(MEDIUM_SIZES[:-1], MEDIUM_SIZES[1:])) * 4 // 2**20,
+                  rows_per_rank * (MEDIUM_SIZES[0] + MEDIUM_SIZES[-1]) * 2 // 2**20)}
+    if parallelism is not None:
+        config["parallelism"] = parallelism
+        config["graph_steps"] = graph_steps
+    return config
+
+
+def small_cpu_baseline(work_name: str) -> dict:
+    """Median seconds per step of the oracle and of eager PyTorch on CPU tensors for a small configuration
+    (100 steps; 10 for the small MLP), state carried from step to step as in training."""
+    import trainkernel_b200 as tk
+    from oracle import interpreter
+    from trainkernel_b200 import workloads
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    steps = 10 if work_name == "c4" else 100
+    result = {"cores": threads, "steps_timed": steps}
+    for kind in ("oracle", "eager"):
+        work = workloads.build(work_name, device="cpu")
+        fn = work.fn()
+        program, _ = tk.capture(fn, (work.state, *work.batches[0]))
+        state = work.state
+        samples = []
+        for i in range(steps + 2):
+            x, t = work.batches[i % len(work.batches)]
+            begin = time.perf_counter()
+            if kind == "oracle":
+                out = interpreter.run(program, (*_leaves(state), x, t))
+                count = len(_leaves(state))
+                new = out[1 + count:]
+                state = tuple(new) if isinstance(state, (tuple, list)) else new[0]
+            else:
+                state = fn(state, x, t)[2]
+            if i >= 2:
+                samples.append(time.perf_counter() - begin)
+        result[f"{kind}_us_per_step"] = round(statistics.median(samples) * 1e6, 1)
+    return result
+
+
+def _percentiles(samples: list[float]) -> dict:
+    ordered = sorted(samples)
+    pick = lambda q: ordered[min(len(ordered) - 1, int(round(q * (len(ordered) - 1))))]  # noqa: E731
+    return {"p10": round(pick(0.1), 2), "p50": round(statistics.median(ordered), 2), "p90": round(pick(0.9), 2),
+            "min": round(ordered[0], 2), "max": round(ordered[-1], 2), "replays": len(ordered)}
+
+
+def small_config_latencies(cpu: bool) -> dict:
+    """Graph-replay latency (us per step; 30 timed replays of a 20-step graph after 10 warm-up replays) of
+    the small configurations, with the CPU path's time per step beside it when `cpu` is set."""
     import trainkernel_b200 as tk
     from trainkernel_b200 import workloads
     result = {}
@@ -227,8 +300,11 @@ def small_config_latencies() -> dict:
         with torch.cuda.graph(graph):
             for i in range(20):
                 compiled(work.state, *work.batches[i % len(work.batches)])
+        for _ in range(10):
+            graph.replay()
+        torch.cuda.synchronize()
         samples = []
-        for _ in range(20):
+        for _ in range(30):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             graph.replay()
@@ -236,13 +312,64 @@ def small_config_latencies() -> dict:
             b.synchronize()
             samples.append(a.elapsed_time(b) * 1e3 / 20)
         compiled.runner.status()
-        p50 = statistics.median(samples)
+        spread = _percentiles(samples)
+        p50 = spread["p50"]
         bound_us = max(work.flops_per_step() / (_peaks()["tflops"] * 1e12), work.bytes_per_step() / (_peaks()["hbm_gbs"] * 1e9)) * 1e6
-        result[work.name] = {"latency_us_p50": round(p50, 2), "steps_per_s": round(1e6 / p50, 1),
+        result[work.name] = {"latency_us_p50": p50, "latency_us": spread, "steps_per_s": round(1e6 / p50, 1),
                              "grid_barriers": compiled.runner.generated.grid_barriers,
                              "barrier": compiled.runner.generated.barrier, "blocks": compiled.runner.module.grid,
                              "roofline_us": round(bound_us, 3), "roofline_frac": round(bound_us / p50, 4)}
+        if cpu:
+            result[work.name]["cpu_baseline"] = small_cpu_baseline(name)
+        del graph, compiled
     return result
+
+
+def parity_check(step, state, initial, graph, losses, last_out, steps: int, world: int, rank: int, device, resident: int) -> dict:
+    """Replay the timed graph once more from the saved initial state and compare every replayed loss, the
+    last step's gradients and the final parameters with the IR-interpreter oracle evaluated on CUDA
+    tensors over the FULL batch (outside any timed region).  The oracle here is the checker only."""
+    import torch.distributed as dist
+    import trainkernel_b200 as tk
+    from oracle import interpreter
+    from trainkernel_b200 import workloads
+    for leaf, saved in zip(_leaves(state), initial):
+        leaf.copy_(saved)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    graph.replay()
+    torch.cuda.synchronize()
+    full = workloads.mlp_workload("oracle", MEDIUM_SIZES, MEDIUM_BATCH, seed=0, device=device, resident=resident)
+    reference = tuple(p.clone() for p in initial)
+    program, _ = tk.capture(full.fn(), (reference, *full.batches[0]))
+    count = len(reference)
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max()) / max(float(b.float().abs().max()), 1e-30)
+
+    worst, where, expected = 0.0, "", None
+    for i in range(steps):
+        expected = interpreter.run(program, (*reference, *full.batches[i % len(full.batches)]))
+        err = rel(losses[i], expected[0])
+        if err > worst:
+            worst, where = err, f"loss of step {i}"
+        reference = tuple(e.clone() for e in expected[1 + count:])
+    for i, (got, want) in enumerate(zip(_leaves(last_out[1]), expected[1:1 + count])):
+        err = rel(got, want)
+        if err > worst:
+            worst, where = err, f"gradient {i} of the last step"
+    for i, (got, want) in enumerate(zip(_leaves(state), reference)):
+        err = rel(got, want)
+        if err > worst:
+            worst, where = err, f"parameter {i} after {steps} steps"
+    if world > 1:
+        collected = torch.tensor([worst], device=device)
+        dist.all_reduce(collected, op=dist.ReduceOp.MAX)
+        worst = float(collected)
+    return {"oracle": "IR interpreter on CUDA tensors, full batch, from the same initial state", "steps": steps,
+            "compared": f"{steps} losses, {count} gradients of the last step, {count} parameters",
+            "worst_rel_error": worst, "worst_at": where, "tolerance": 2e-2, "passed": bool(worst <= 2e-2)}
 
 
 def main() -> None:
@@ -254,6 +381,8 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-small-configs", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--no-parity", action="store_true", help="skip the oracle check of the replayed steps (for profiler runs)")
+    parser.add_argument("--latency-replays", type=int, default=30, help="timed graph replays for the latency distribution (after 10 warm-ups)")
     parser.add_argument("--workload", default="c5", choices=["c5", "c5_half"],
                         help="c5_half (2048-4096-4096-4096-2048, batch 4096) is the small case used for ncu captures")
     parser.add_argument("--eager", action="store_true", help="launch the timed steps directly instead of replaying a CUDA graph")
@@ -340,26 +469,33 @@ def main() -> None:
                 failed += 1
             dist.all_reduce(failed, op=dist.ReduceOp.MAX)
             if int(failed.item()):
+                step.close()                 # unmap the peer-mapped buffer on every rank before a new one is made
+                del step
+                barrier()
                 work = workloads.mlp_workload(work.name, MEDIUM_SIZES, MEDIUM_BATCH, seed=0, device=device, rows=rows)
                 state = work.state
                 step = dp.FusedShardedTrainingStep(work.fn(), (state, *work.batches[0]), multicast=False)
                 status, generated = step.status, step.generated
                 step(state, *work.batches[0])
     barrier()
+    initial = None if args.no_parity else [p.clone() for p in _leaves(state)]
     losses = []
+    last_out = [None]
     if args.eager:
         class _Eager:
             def replay(self):
                 losses.clear()
                 for i in range(steps):
-                    losses.append(step(state, *work.batches[i % len(work.batches)])[0])
+                    last_out[0] = step(state, *work.batches[i % len(work.batches)])
+                    losses.append(last_out[0][0].clone())
         graph = _Eager()
     else:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             for i in range(steps):
                 out = step(state, *work.batches[i % len(work.batches)])
-                losses.append(out[0])
+                losses.append(out[0].clone() if world > 1 else out[0])   # sharded steps reuse one loss buffer
+                last_out[0] = out
     graph.replay()                       # one untimed replay: graph upload, allocator settled
     barrier()
     launches_before = runtime.library().tk_launch_count()
@@ -375,26 +511,17 @@ def main() -> None:
         end.record()
         barrier()
         elapsed_ms = begin.elapsed_time(end)
-        # further replays only for the latency distribution
+        # further replays only for the latency distribution: 10 warm-ups, then `--latency-replays` timed ones
         samples = [elapsed_ms / steps * 1e3]
-        for _ in range(4):
+        for i in range(10 + max(0, args.latency_replays - 1)):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             barrier()
             a.record()
             graph.replay()
             b.record()
             barrier()
-            samples.append(a.elapsed_time(b) / steps * 1e3)
-        # a short step leaves the 20 ms clock sampler few samples: keep replaying (untimed) until it has a handful
-        extra = 0
-        while world == 1 and sampler.process is not None and sampler.count() < 5 and extra < 50:
-            graph.replay()
-            torch.cuda.synchronize()
-            extra += 1
-        if world > 1:
-            for _ in range(3):           # the same count on every rank: the replays synchronise with each other
-                graph.replay()
-            barrier()
+            if i >= 10:
+                samples.append(a.elapsed_time(b) / steps * 1e3)
     status()
     clocks = sampler.summary()
     if world > 1:
@@ -404,8 +531,7 @@ def main() -> None:
         sample_tensor = torch.tensor(samples, device=device)
         dist.all_reduce(sample_tensor, op=dist.ReduceOp.MAX)
         samples = [float(v) for v in sample_tensor]
-    final_loss = float(losses[-1])
-    assert final_loss == final_loss and abs(final_loss) < 1e6, "loss diverged"
+    assert bool(torch.isfinite(losses[-1])), "loss diverged"
 
     # per-rank gradient-kernel duration for the roofline (CUDA events on the launching stream)
     kernel_ms = elapsed_ms / steps
@@ -424,7 +550,7 @@ def main() -> None:
     local_flops = 4 * work.batch * work.weight_elements + 2 * work.batch * (work.weight_elements - MEDIUM_SIZES[0] * MEDIUM_SIZES[1])
     achieved = local_flops / (kernel_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": round(achieved, 1), "peak": peaks["tflops"], "unit": "TFLOP/s",
-                "frac": round(achieved / peaks["tflops"], 4), "traffic": MEASURED_TRAFFIC_BYTES if world == 1 else None,
+                "frac": round(achieved / peaks["tflops"], 4), "traffic": measured_traffic(generated) if world == 1 else None,
                 "peak_source": peaks["source"], "kernel_ms": round(kernel_ms, 4),
                 "algorithmic_flops_per_launch": local_flops, "frac_of_burst_peak": round(achieved / peaks["tflops_burst"], 4)}
 
@@ -433,43 +559,57 @@ def main() -> None:
     if not args.no_e2e:
         e2e = measure_e2e(step, state, work, steps, world, device)
 
+    parity = None
+    if not args.no_parity:
+        parity = parity_check(step, state, initial, graph, losses, last_out[0], steps, world, rank, device, len(work.batches))
+        if not parity["passed"]:
+            print(f"[bench] PARITY FAILED: {parity}", file=sys.stderr)
+    final_loss = float(losses[-1])
+
+    parallelism = (f"dp{world} (batch-sharded, BF16 gradient mean exchanged inside the step kernel over NVLink, "
+                   + ("multimem.ld_reduce / multimem.st through the NVSwitch multicast mapping)" if getattr(step, "multicast", False)
+                      else "peer stores into the owners' staging areas)")
+                   if world > 1 and args.dp == "fused" else
+                   f"dp{world} (batch-sharded, NCCL all-reduce of the BF16 gradients between two kernels)" if world > 1
+                   else "single GPU, one kernel per step")
     line = {
         "metric": "captured_step_throughput", "value": steps / (elapsed_ms * 1e-3), "unit": "steps/s",
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": elapsed_ms / steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.workload} medium MLP {'-'.join(map(str, MEDIUM_SIZES))}, global batch {MEDIUM_BATCH}, BF16 compute / FP32 master, SGD lr 1e-3",
-                   "global_batch": MEDIUM_BATCH, "rows_per_rank": work.batch, "resident_batches": len(work.batches),
-                   "parallelism": (f"dp{world} (batch-sharded, BF16 gradient mean exchanged inside the step kernel over NVLink, "
-                                   + ("multimem.ld_reduce / multimem.st through the NVSwitch multicast mapping)" if getattr(step, "multicast", False)
-                                      else "peer stores into the owners' staging areas)")
-                                   if world > 1 and args.dp == "fused" else
-                                   f"dp{world} (batch-sharded, NCCL all-reduce of the BF16 gradients between two kernels)" if world > 1
-                                   else "single GPU, one kernel per step"),
-                   "l2": "inputs larger than L2 (FP32 weights %d MB, %d MB per batch)" % (work.weight_elements * 4 // 2**20, work.batch * (MEDIUM_SIZES[0] + MEDIUM_SIZES[-1]) * 2 // 2**20),
-                   "graph_steps": 0 if args.eager else steps},
-        "latency_us": {"p50": round(statistics.median(samples), 1), "min": round(min(samples), 1), "max": round(max(samples), 1),
-                       "replays": len(samples)},
+        "config": _config(args.workload, world, work.batch, len(work.batches), parallelism, 0 if args.eager else steps),
+        "latency_us": _percentiles(samples),
         "clocks": clocks, "roofline": roofline, "e2e": e2e,
         "gpu_launches": steps * kernels_per_step,
         "kernel": {"stages": generated.stages, "grid_barriers": generated.grid_barriers, "grid": generated.grid,
                    "tensor_core_units": generated.tensor_core_operations, "workspace_bytes": generated.workspace_bytes},
+        "parity_checked": bool(parity and parity["passed"]), "parity": parity,
         "final_loss": final_loss,
         "shim_launches_recorded": int(runtime.library().tk_launch_count() - launches_before),
     }
-    if world == 1 and rank == 0:
-        if not args.no_small_configs:
-            line["other_configs"] = small_config_latencies()
-        if not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(1, 1)
-    if rank == 0:
-        print(json.dumps(line), flush=True)
     if world > 1:
-        # Tearing an NCCL communicator down while CUDA graphs that captured its collectives are still
-        # alive can block forever; every rank has its result, so leave without the teardown.
+        # Leave in order: the graphs first (they pin the communicator's kernels), then the step (which
+        # unmaps the peer-mapped buffer and its multicast binding), and only then the process group, so
+        # that no rank's memory goes away while a peer still has it mapped.
+        del graph, out, last_out, losses
+        if hasattr(step, "close"):
+            step.close()
+        del step
+        import gc
+        gc.collect()
         barrier()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
+        guard = threading.Timer(60.0, lambda: os._exit(0))     # a teardown that blocks must not hold the box
+        guard.daemon = True
+        guard.start()
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        dist.destroy_process_group()
+        guard.cancel()
+        return
+    if not args.no_small_configs:
+        line["other_configs"] = small_config_latencies(cpu=not args.no_cpu_baseline)
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line), flush=True)
 
 
 def measure_e2e(step, state, work, steps: int, world: int, device) -> dict:

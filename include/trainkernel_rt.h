@@ -62,6 +62,28 @@ int tk_module_load(const void* cubin, size_t cubin_bytes, const char* entry, int
 int tk_module_launch(tk_module* module, const void* const* inputs, void* const* outputs,
                      void* workspace, int grid, void* stream);
 
+/* tk_module_launch with launch flags.  TK_LAUNCH_TRUST_CARRIED tells a kernel that keeps derived values
+ * from one launch to the next (the BF16 copies of FP32 master weights, written by the step that updated the
+ * masters) that the caller has not modified the in-place state since this module's previous launch, so the
+ * kernel may skip recomputing them.  The flag is ignored (the values are recomputed) by the first launch ever,
+ * after tk_module_reset / tk_module_invalidate_carried, and by the first launch recorded into each stream
+ * capture, so a replayed CUDA graph always starts from the caller's state.  tk_module_launch passes no flags.
+ * No counterpart in the reference, which recasts every weight in every step (trainkernel/codegen.py:419-423). */
+#define TK_LAUNCH_TRUST_CARRIED 1u
+int tk_module_launch_flags(tk_module* module, const void* const* inputs, void* const* outputs,
+                           void* workspace, int grid, void* stream, uint32_t flags);
+
+/* Enqueue on `stream` the invalidation of the values carried over between launches (see above): for a
+ * caller that rewrites the state by means the host cannot see.  No counterpart in the reference. */
+int tk_module_invalidate_carried(tk_module* module, void* stream);
+
+/* Device ordinal the module was loaded on; the workspace size its kernel's plan needs, as recorded by
+ * whoever loaded it (0 when never recorded).  Used by launch paths that must check what they are handed.
+ * No counterpart in the reference (its launch derives both from the workspace tensor, trainkernel/codegen.py:866). */
+int tk_module_device(tk_module* module, int* out);
+int tk_module_set_workspace_bytes(tk_module* module, size_t bytes);
+int tk_module_workspace_bytes(tk_module* module, size_t* out);
+
 /* {registers per thread, local bytes per thread, static + dynamic shared bytes per block,
  * resident blocks per SM}.  Replaces `resource_usage()` (reference: trainkernel/codegen.py:889-895). */
 int tk_module_resource_usage(tk_module* module, int64_t out[4]);
@@ -84,7 +106,10 @@ int tk_module_set_cooperative(tk_module* module, int enabled);
 int tk_module_max_coresident_blocks(tk_module* module, int* out);
 
 /* Synchronise `stream`, then copy the kernel's status words {code, stage, block, detail}.
- * Returns TK_E_KERNEL when code != 0.  (The reference cannot report a stuck barrier:
+ * Returns TK_E_KERNEL when code != 0; from then on every launch of this module is refused with TK_E_KERNEL
+ * until tk_module_reset, because a kernel that gave up on a wait leaves partial outputs behind and later
+ * launches would give up early too.  The status words are sticky on the device, so callers of a long loop
+ * should poll this every few steps.  (The reference cannot report a stuck barrier:
  * cooperative_groups grid.sync() has no timeout, reference: trainkernel/codegen.py:833-836.) */
 int tk_module_status(tk_module* module, void* stream, uint32_t out[4]);
 
@@ -98,9 +123,12 @@ int tk_module_set_timeout(tk_module* module, uint64_t nanoseconds);
  * tests that make a barrier time out on purpose without hanging the device. */
 int tk_module_set_expected_arrivals(tk_module* module, uint32_t arrivals);
 
-/* Synchronise `stream`, then copy up to `count` per-stage %globaltimer stamps written by a
- * kernel generated with stage stamps (the built-in form of the reference's source-patching
- * stage profiler, reference: scripts/profile_stages.py:36-54). */
+/* Synchronise `stream`, then copy up to `count` (at most 256) 64-bit stamps written by a kernel generated
+ * with stage stamps (the built-in form of the reference's source-patching stage profiler, reference:
+ * scripts/profile_stages.py:36-54).  Layout, all %globaltimer nanoseconds unless noted: [0, 64) block 0
+ * leaves stage boundary s (entry 0: kernel start, entry `stages`: kernel end); [64, 128) block 0 arrives at
+ * grid barrier k; [128, 192) the last block arrives at grid barrier k; [192, 248) nanoseconds block 0 waited
+ * for its peers' flags before stage s (multi-GPU kernels); [248, 254) role-level trace of one tile. */
 int tk_module_stage_stamps(tk_module* module, void* stream, uint64_t* out, int count);
 
 void tk_module_unload(tk_module* module);

@@ -1,21 +1,27 @@
 """Multi-GPU check of the sharded training step, run as one process per GPU under torchrun.
 
-Every rank compiles the full-batch step (the single-GPU kernel, as the yardstick) and the
-batch-sharded step in each exchange form the box supports, runs a few steps of each from the same
-state, and compares loss, gradients and updated state:
+Every rank evaluates the ORACLE (the IR interpreter, on CUDA tensors) on the full batch for a few
+steps, then runs the batch-sharded step in each form the box supports from the same initial state,
+and compares every step's loss, the last step's gradients and the final parameters:
 
-    sharded form  vs  full batch        within the 16-bit-compute bound (2e-2 relative)
-    form          vs  form              near-equal (the forms differ only in FP32 summation order)
-    rank          vs  rank              bit-identical replicas (checksums gathered over the group)
+    sharded form  vs  oracle, full batch     within the 16-bit-compute bound (2e-2 relative)
+    sharded form  vs  this repository's single-GPU kernel on the full batch (same bound; informative)
+    form          vs  form                   near-equal (the forms differ only in FP32 summation order)
+    rank          vs  rank                   bit-identical replicas (bit-pattern sums gathered over the group)
 
+Forms: the one-kernel step with peer stores ("scatter"), the one-kernel step through the NVSwitch
+multicast mapping ("multicast", where the box has one), and the two-kernel NCCL baseline ("nccl").
+For the small workloads the host (CPU) oracle is evaluated too and its distance reported.
 Rank 0 prints one JSON line; every rank exits non-zero on a failed comparison.
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import sys
+import threading
 from pathlib import Path
 
 import torch
@@ -24,41 +30,75 @@ import torch.distributed as dist
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 import trainkernel_b200 as tk  # noqa: E402
+from oracle import interpreter  # noqa: E402
 from trainkernel_b200 import dp, workloads  # noqa: E402
 
-SIZES = {"c2": ((128, 256, 128), 16), "c4": ((1024, 2048, 2048, 1024), 512), "wide": ((512, 1024, 768, 512), 1024)}
+SIZES = {"c2": ((128, 256, 128), 16), "c4": ((1024, 2048, 2048, 1024), 512), "wide": ((512, 1024, 768, 512), 1024),
+         "c5": ((4096, 8192, 8192, 8192, 4096), 8192)}
+HOST_ORACLE = ("c2", "wide")          # small enough for the CPU interpreter inside a test
+TOLERANCE = 2e-2
 
 
 def rel(a: torch.Tensor, b: torch.Tensor) -> float:
-    return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+    a, b = a.float(), b.float().to(a.device)
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
 
 
 def run_steps(step, state, batches, steps):
-    out = None
+    """Run `steps` steps; returns (losses, last gradients, final parameters), all cloned."""
+    losses, out = [], None
     for i in range(steps):
         out = step(state, *batches[i % len(batches)])
+        losses.append(out[0].clone())
     torch.cuda.synchronize()
-    loss, grads, _ = out
-    return loss.clone(), [g.clone() for g in grads], [p.clone() for p in state]
+    return losses, [g.clone() for g in out[1]], [p.clone() for p in state]
+
+
+def oracle_steps(fn, state, batches, steps):
+    """The same steps through the IR interpreter on whatever device `state` lives on."""
+    program, _ = tk.capture(fn, (tuple(state), *batches[0]))
+    count = len(state)
+    current, losses, expected = tuple(state), [], None
+    for i in range(steps):
+        expected = interpreter.run(program, (*current, *batches[i % len(batches)]))
+        losses.append(expected[0].clone())
+        current = tuple(e.clone() for e in expected[1 + count:])
+    return losses, [g.clone() for g in expected[1:1 + count]], list(current)
+
+
+def distance(result, reference) -> float:
+    losses, grads, params = result
+    return max([rel(a, b) for a, b in zip(losses, reference[0])] + [rel(a, b) for a, b in zip(grads, reference[1])]
+               + [rel(a, b) for a, b in zip(params, reference[2])])
+
+
+def _meta_program(sizes, batch):
+    state = []
+    for fan_in, fan_out in zip(sizes[:-1], sizes[1:]):
+        state += [torch.empty(fan_in, fan_out, device="meta"), torch.empty(fan_out, device="meta")]
+    x = torch.empty(batch, sizes[0], dtype=torch.bfloat16, device="meta")
+    t = torch.empty(batch, sizes[-1], dtype=torch.bfloat16, device="meta")
+    program, _ = tk.capture(lambda s, xx, tt: workloads.mlp_master_step(s, xx, tt, 1e-3), (tuple(state), x, t))
+    return program
 
 
 def kernel_sources() -> dict[str, str]:
     """Generated sources of every kernel this check launches at 2 and 4 ranks (for ahead-of-time compilation)."""
     from trainkernel_b200 import codegen
-    from trainkernel_b200.passes import insert_gradient_exchange
+    from trainkernel_b200.passes import insert_gradient_exchange, split_at_gradients
     sources = {}
     for name, (sizes, batch) in SIZES.items():
         count = 2 * (len(sizes) - 1)
         inplace = {1 + count + i: i for i in range(count)}
-        full = workloads.mlp_workload("full", sizes, batch, seed=3, resident=1)
-        program, _ = tk.capture(full.fn(), (full.state, *full.batches[0]))
-        sources[f"{name}_full"] = codegen.generate(program, inplace_outputs=inplace).source
+        sources[f"{name}_full"] = codegen.generate(_meta_program(sizes, batch), inplace_outputs=inplace).source
         for world in (2, 4):
-            shard = workloads.mlp_workload("shard", sizes, batch, seed=3, resident=1, rows=dp.shard_rows(batch, 0, world))
-            program, _ = tk.capture(shard.fn(), (shard.state, *shard.batches[0]))
+            program = _meta_program(sizes, batch // world)
             for multicast in (False, True):
                 sources[f"{name}_w{world}_{multicast}"] = codegen.generate(insert_gradient_exchange(program, count), inplace_outputs=inplace,
                                                                           world=world, multicast=multicast).source
+            gradient, update = split_at_gradients(program, count, narrow_exchange=True)
+            sources[f"{name}_w{world}_gradient"] = codegen.generate(gradient).source
+            sources[f"{name}_w{world}_update"] = codegen.generate(update, inplace_outputs={count + i: i for i in range(count)}).source
     return sources
 
 
@@ -70,33 +110,57 @@ def main() -> int:
     world, rank, local = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    torch.backends.cuda.matmul.allow_tf32 = False
     dist.init_process_group("nccl", device_id=device)
     sizes, batch = SIZES[args.workload]
     full = workloads.mlp_workload("full", sizes, batch, seed=3, device=device, resident=2)
     shard = workloads.mlp_workload("shard", sizes, batch, seed=3, device=device, resident=2, rows=dp.shard_rows(batch, rank, world))
     failures: list[str] = []
-    report: dict = {"workload": args.workload, "world": world, "steps": args.steps}
+    report: dict = {"workload": args.workload, "world": world, "steps": args.steps, "tolerance": TOLERANCE,
+                    "oracle": "IR interpreter on CUDA tensors, full batch"}
+
+    expected = oracle_steps(full.fn(), [p.clone() for p in full.state], full.batches, args.steps)
+    if args.workload in HOST_ORACLE:
+        host = workloads.mlp_workload("host", sizes, batch, seed=3, device="cpu", resident=2)
+        expected_host = oracle_steps(host.fn(), [p.clone() for p in host.state], host.batches, args.steps)
+        report["device_oracle_vs_host_oracle"] = distance(expected, expected_host)
+    else:
+        expected_host = None
 
     state = tuple(p.clone() for p in full.state)
-    yardstick = run_steps(tk.compile_training(full.fn(), (state, *full.batches[0])), state, full.batches, args.steps)
+    single = tk.compile_training(full.fn(), (state, *full.batches[0]))
+    yardstick = run_steps(single, state, full.batches, args.steps)
+    single.runner.status()
+    report["single_gpu_kernel_vs_oracle"] = distance(yardstick, expected)
+    del single
 
     results = {}
-    for name, multicast in (("scatter", False), ("multicast", True)):
+    for name in ("scatter", "multicast", "nccl"):
         state = tuple(p.clone() for p in shard.state)
         try:
-            step = dp.FusedShardedTrainingStep(shard.fn(), (state, *shard.batches[0]), multicast=multicast)
+            if name == "nccl":
+                step = dp.ShardedTrainingStep(shard.fn(), (state, *shard.batches[0]))
+            else:
+                step = dp.FusedShardedTrainingStep(shard.fn(), (state, *shard.batches[0]), multicast=(name == "multicast"))
         except RuntimeError as error:                          # raised on every rank alike
             if "no multicast mapping" not in str(error):
                 raise
-            continue                                           # no multicast mapping on this box: one form only
+            continue                                           # no multicast mapping on this box
         results[name] = run_steps(step, state, shard.batches, args.steps)
         step.status()
-        loss, grads, params = results[name]
-        worst = max([rel(loss, yardstick[0])] + [rel(a, b) for a, b in zip(grads, yardstick[1])] + [rel(a, b) for a, b in zip(params, yardstick[2])])
-        report[f"{name}_vs_full_batch"] = worst
-        if not worst <= 2e-2:
-            failures.append(f"{name}: {worst:.3e} from the full-batch step")
-        # replicas: a float64 checksum and an exact bit pattern sum of all state must agree on every rank
+        step.close()
+        del step
+        gc.collect()
+        dist.barrier()
+        worst = distance(results[name], expected)
+        report[f"{name}_vs_oracle"] = worst
+        report[f"{name}_vs_single_gpu_kernel"] = distance(results[name], yardstick)
+        if expected_host is not None:
+            report[f"{name}_vs_host_oracle"] = distance(results[name], expected_host)
+        if not worst <= TOLERANCE:
+            failures.append(f"{name}: {worst:.3e} from the oracle on the full batch")
+        # replicas: the exact bit-pattern sums of all parameters and gradients must agree on every rank
+        _, grads, params = results[name]
         bits = torch.stack([p.view(torch.int32).to(torch.int64).sum() for p in params] + [g.view(torch.int32).to(torch.int64).sum() for g in grads])
         gathered = [torch.empty_like(bits) for _ in range(world)]
         dist.all_gather(gathered, bits)
@@ -104,20 +168,28 @@ def main() -> int:
         report[f"{name}_replicas_identical"] = identical
         if not identical:
             failures.append(f"{name}: replicas differ")
-    if len(results) == 2:
-        a, b = results["scatter"], results["multicast"]
-        gap = max([rel(a[0], b[0])] + [rel(x, y) for x, y in zip(a[1], b[1])] + [rel(x, y) for x, y in zip(a[2], b[2])])
-        report["multicast_vs_scatter"] = gap
-        if not gap <= 1e-2:                                    # one BF16 ulp of the largest element at most
-            failures.append(f"multicast and scatter forms differ by {gap:.3e}")
+    for other in ("multicast", "nccl"):
+        if other in results and "scatter" in results:
+            gap = distance(results[other], results["scatter"])
+            report[f"{other}_vs_scatter"] = gap
+            if not gap <= 1e-2:                                # one BF16 ulp of the largest element at most
+                failures.append(f"{other} and scatter forms differ by {gap:.3e}")
     report["forms"] = sorted(results)
     report["failures"] = failures
+    everyone = torch.tensor([len(failures)], device=device)
+    dist.all_reduce(everyone, op=dist.ReduceOp.MAX)
     if rank == 0:
         print(json.dumps(report), flush=True)
-    dist.barrier()
+    # leave in order: every step object (and with it every peer mapping) is gone; now the group
     torch.cuda.synchronize()
-    os._exit(1 if failures else 0)     # graphs and symmetric buffers outlive an orderly teardown of the group
+    dist.barrier()
+    guard = threading.Timer(60.0, lambda: os._exit(1 if int(everyone) else 0))   # a blocked teardown must not hold the box
+    guard.daemon = True
+    guard.start()
+    dist.destroy_process_group()
+    guard.cancel()
+    return 1 if int(everyone) else 0
 
 
 if __name__ == "__main__":
-    main()
+    sys.exit(main())

@@ -39,7 +39,7 @@ CASES = [
     ("c3_seed0", "c3", 0, 100),
     ("c3_seed1", "c3", 1, 100),
     ("c3_seed2", "c3", 2, 100),
-    ("c4_seed0", "c4", 0, 4),
+    ("c4_seed0", "c4", 0, 100),
     ("gemv_seed0", "gemv", 0, 100),
 ]
 

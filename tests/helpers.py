@@ -52,7 +52,7 @@ def l2_error(actual: torch.Tensor, expected: torch.Tensor) -> float:
     return float((a - b).norm()) / max(float(b.norm()), 1e-30)
 
 
-def assert_step_close(actual, expected_cpu, program, device_inputs, tol: float, label: str = "") -> None:
+def assert_step_close(actual, expected_cpu, program, device_inputs, tol: float, label: str = "", max_fallbacks: int = 2) -> list[dict]:
     """Parity of one training step against the IR oracle.
 
     The bound is `tol` on max|a-b|/max|b| against the oracle evaluated on the host.  One
@@ -61,12 +61,18 @@ def assert_step_close(actual, expected_cpu, program, device_inputs, tol: float, 
     the GPU (different FP32 summation order inside the matmul), which moves a whole column
     of the next weight gradient by one of its 1/batch terms.  When the host comparison
     fails for a 16-bit-compute step, the same oracle is therefore also evaluated on the
-    device (same IR, same rounding points, cuBLAS summation order); the step passes if it
+    device (same IR, same rounding points, cuBLAS summation order); the output passes if it
     is within `tol` of that evaluation and within `tol` of the host oracle in the L2 norm.
+
+    Every output that needed this second comparison is printed and returned (index, host error,
+    device-oracle error, L2 error, fraction of elements beyond the bound); at most
+    `max_fallbacks` outputs of a step may need it, and in each of them the elements beyond
+    the bound must be a small minority (a few flipped columns, not a wrong tensor).
     """
     got, _ = tree_flatten(actual)
     assert len(got) == len(expected_cpu), f"{label}: output count"
     on_device = None
+    fallbacks: list[dict] = []
     for index, (a, b) in enumerate(zip(got, expected_cpu)):
         assert tuple(a.shape) == tuple(b.shape) and a.dtype == b.dtype, f"{label}: output {index} signature"
         assert bool(torch.isfinite(a.float()).all()), f"{label}: output {index} is not finite"
@@ -77,6 +83,15 @@ def assert_step_close(actual, expected_cpu, program, device_inputs, tol: float, 
         if on_device is None:
             flat, _ = tree_flatten(device_inputs)
             on_device = interpreter.run(program, flat)
-        assert l2_error(a, b) <= tol, f"{label}: output {index} L2 relative error {l2_error(a, b):.3e}"
+        l2 = l2_error(a, b)
+        assert l2 <= tol, f"{label}: output {index} L2 relative error {l2:.3e}"
         err_device = rel_error(a, on_device[index])
         assert err_device <= tol, f"{label}: output {index} relative error {err:.3e} (host) / {err_device:.3e} (device oracle)"
+        host = b.detach().float()
+        beyond = float(((a.detach().float().cpu() - host).abs() > tol * float(host.abs().max())).float().mean())
+        assert beyond <= 0.02, f"{label}: output {index}: {beyond:.2%} of the elements are beyond the bound, not a few flipped ReLU masks"
+        record = {"output": index, "host_oracle": err, "device_oracle": err_device, "l2": l2, "fraction_beyond_bound": beyond}
+        print(f"[parity] {label}: output {index} passed through the device-oracle comparison: {record}")
+        fallbacks.append(record)
+    assert len(fallbacks) <= max_fallbacks, f"{label}: {len(fallbacks)} outputs needed the device-oracle comparison: {fallbacks}"
+    return fallbacks

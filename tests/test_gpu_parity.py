@@ -50,6 +50,30 @@ def test_training_step_matches_oracle(name):
         assert torch.equal(leaf, new)
 
 
+@pytest.mark.parametrize("name", ["c1", "c2", "c3", "c4"])
+def test_training_step_matches_eager_pytorch_on_the_gpu(name):
+    """The second yardstick beside the IR oracle: the step function itself, run eagerly by PyTorch on
+    the same device and the same seeded inputs (TF32 and reduced-precision reductions off)."""
+    from tests import cases
+    previous = (torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction, torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction)
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
+    try:
+        compiled, inputs, _, _ = compile_case(name)
+        fn, eager_inputs, _, _ = cases.build(name, "cuda")
+        loss, grads, updated = fn(*eager_inputs)
+        expected = [loss, *tree_flatten(grads)[0], *tree_flatten(updated)[0]]
+        out = compiled(*inputs)
+        compiled.runner.status()
+        tol = REL_TOL[_compute_dtype(inputs)]
+        if tol < 1e-4:
+            tol = 2e-5          # two different FP32 summation orders against each other, not against the exact host sum
+        assert_outputs_close(out, expected, tol, f"{name} against eager PyTorch")
+    finally:
+        (torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction,
+         torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction) = previous
+
+
 @pytest.mark.parametrize("name", GENERAL_CASES)
 def test_general_subset_matches_oracle(name):
     compiled, inputs, cpu_inputs, program = compile_case(name)

@@ -16,7 +16,7 @@ SAMPLE = 2048
 # same torch CPU kernels, so differences come only from a different host CPU's vector width.
 CASES = [("c1_seed0", "c1", 0, 100, 2e-6), ("c2_seed0", "c2", 0, 100, 2e-3), ("c2_seed1", "c2", 1, 100, 2e-3),
          ("c2_seed2", "c2", 2, 100, 2e-3), ("c3_seed0", "c3", 0, 20, 2e-3), ("c3_seed1", "c3", 1, 5, 2e-3),
-         ("c3_seed2", "c3", 2, 5, 2e-3), ("c4_seed0", "c4", 0, 1, 2e-3), ("gemv_seed0", "gemv", 0, 100, 2e-3)]
+         ("c3_seed2", "c3", 2, 5, 2e-3), ("c4_seed0", "c4", 0, 100, 2e-3), ("gemv_seed0", "gemv", 0, 100, 2e-3)]
 
 
 def _leaves(state):

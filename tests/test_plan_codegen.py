@@ -203,3 +203,31 @@ def test_small_programs_run_as_one_cluster_with_the_hardware_barrier():
     # a kernel that exchanges with peers keeps the grid barrier (its flags are raised after grid barriers)
     from trainkernel_b200.passes import insert_gradient_exchange
     assert generate(insert_gradient_exchange(program, 4), inplace_outputs=inplace, world=2).barrier == "grid"
+
+
+def _deep_mlp_program(layers: int):
+    sizes = tuple([32] * (layers + 1))
+    work = workloads.mlp_workload("deep", sizes, 8, seed=0, resident=1)
+    program, _ = tk.capture(work.fn(), (work.state, *work.batches[0]))
+    n = len(work.state)
+    return program, {1 + n + i: i for i in range(n)}, n
+
+
+def test_fixed_size_stage_tables_are_guarded():
+    """The stamp area holds 55 stages and the symmetric header 64 barrier flags per rank: a program
+    beyond either limit is rejected when the kernel is generated, not when it overruns a table."""
+    from trainkernel_b200.passes import insert_gradient_exchange
+    program, inplace, n = _deep_mlp_program(34)
+    plain = generate(program, inplace_outputs=inplace)
+    assert plain.stages > codegen.MAX_STAMPED_STAGES           # fine without stamps
+    with pytest.raises(ValueError, match="stage stamps cover at most"):
+        generate(program, inplace_outputs=inplace, stage_stamps=True)
+    exchanged = insert_gradient_exchange(program, n)
+    with pytest.raises(ValueError, match="at most 64 grid barriers"):
+        generate(exchanged, inplace_outputs=inplace, world=2)
+    small, small_inplace, _ = _deep_mlp_program(2)
+    with pytest.raises(ValueError, match="trace_stage needs"):
+        generate(small, inplace_outputs=small_inplace, trace_stage=1)
+    with pytest.raises(ValueError, match="trace_stage needs"):
+        generate(small, inplace_outputs=small_inplace, stage_stamps=True, trace_stage=99)
+    assert generate(small, inplace_outputs=small_inplace, stage_stamps=True, trace_stage=1).stages <= codegen.MAX_STAMPED_STAGES

@@ -18,7 +18,10 @@ from dataclasses import dataclass, field
 from math import prod
 
 from .ir import Operation, Program, TensorSpec, row_major, validate
-from .plan import (ELEMENT_BYTES, THREADS, Access, Apply, Const, Iota, Load, Plan, Planner, Ref, Unit, point_unroll)
+from .plan import (ELEMENT_BYTES, SYM_HEADER, THREADS, Access, Apply, Const, Iota, Load, Plan, Planner, Ref, Unit, point_unroll)
+
+MAX_STAMPED_STAGES = 55          # stamp area: 64 words per table, the peer-wait table shares its block with the role trace
+FLAG_WORDS_PER_RANK = 64         # cross-rank "passed barrier k" words per rank in the symmetric header
 
 CTYPE = {"float32": "float", "float16": "__half", "bfloat16": "__nv_bfloat16", "int64": "long long", "int32": "int", "bool": "bool"}
 ROUND = {"float32": "tk::F32", "float16": "tk::F16", "bfloat16": "tk::BF16", "int64": "tk::I64", "int32": "tk::I32", "bool": "tk::B8"}
@@ -746,7 +749,7 @@ class _Emitter:
             "    uint64_t* stamps;",
             "    uint64_t timeout_ns;",
             "    uint32_t arrivals;",
-            "    uint32_t reserved;",
+            "    uint32_t flags;",
             "};",
             "",
         ]
@@ -762,6 +765,9 @@ class _Emitter:
             "    tk::ctx_init2(c, P.sync, P.status, P.timeout_ns, P.arrivals, &shared_state, dyn_smem);" if plan.two_cta else
             f"    tk::ctx_init(c, P.sync, P.status, P.timeout_ns, P.arrivals, &shared_state, dyn_smem, {use_tc});",
         ]
+        entry.append("    c.flags = P.flags;")
+        if stage_stamps:
+            entry.append("    c.stamps = P.stamps;")
         if plan.uses_tc:
             entry.append("    c.epi = &epi_stage.t[0][0][0];")
         if n_maps_used:
@@ -862,9 +868,11 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     thread-block cluster of at most 8 blocks whose stages end in the hardware cluster barrier instead
     of the barrier through global memory; `GeneratedKernel.barrier` says which one a kernel uses.
 
-    `trace_stage=s` (with `stage_stamps=True`) also records six role-level timestamps of the first
-    single-CTA tensor-core tile of stage `s` in stamp slots 32..37 (`CompiledProgram.stage_stamps`
-    returns them after the per-stage values when asked for 38 entries).
+    `stage_stamps=True` makes block 0 record the global timer at every stage boundary and makes every
+    grid barrier record when block 0 and when the last block arrived (`CompiledProgram.stage_stamps`,
+    `CompiledProgram.barrier_stalls`); the stamp area has room for 55 stages.  `trace_stage=s` (with
+    `stage_stamps=True`) also records six role-level timestamps of the first single-CTA tensor-core
+    tile of stage `s` (`CompiledProgram.role_trace`).
 
     With `world > 1` the kernel takes `1 + world` extra inputs after the program's own: this rank's
     symmetric buffer, then every rank's mapping of it in rank order.  `multicast=True` adds one more,
@@ -883,6 +891,17 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
                         fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n,
                         two_cta=two_cta, world=world, background=background, multicast=multicast,
                         cluster_barrier=cluster_barrier)
+    # Fixed-size tables the kernel indexes by stage or barrier number: the stamp area, and (with peers) the
+    # 64 flag words per rank in the symmetric buffer's header, laid out from word 16.
+    if stage_stamps and plan.stages > MAX_STAMPED_STAGES:
+        raise ValueError(f"trainkernel: stage stamps cover at most {MAX_STAMPED_STAGES} stages; this program has {plan.stages}")
+    if trace_stage is not None and (not stage_stamps or not 0 <= trace_stage < plan.stages):
+        raise ValueError("trainkernel: trace_stage needs stage_stamps=True and a stage of this program")
+    if plan.world > 1 or plan.symmetric_bytes:
+        if plan.stages - 1 > FLAG_WORDS_PER_RANK:
+            raise ValueError(f"trainkernel: a kernel that exchanges with peers can have at most {FLAG_WORDS_PER_RANK} grid barriers; this program has {plan.stages - 1}")
+        if 4 * (16 + FLAG_WORDS_PER_RANK * plan.world) > SYM_HEADER:
+            raise ValueError("trainkernel: the symmetric buffer's header has no room for this many ranks")
     emitter = _Emitter(plan)
     emitter.trace_stage = trace_stage
     if raster_group is not None:

@@ -43,6 +43,14 @@ constexpr int kTmemCols = 512;         // two 256-column FP32 accumulators
 constexpr int kDynSmem = 4 * (kSlotA + kMaxBN * BK * 2) + 1024;  // 192 KiB for any ring shape, +1024 for manual alignment
 static_assert(kStages * kSlotBytes + 1024 <= kDynSmem && kStages <= kMaxStages, "ring does not fit");
 
+// Stamp area (64-bit words) of kernels generated with stage stamps.
+constexpr int kStampArrive = 64;       // + k: block 0 arrives at grid barrier k
+constexpr int kStampLast = 128;        // + k: the last block arrives at grid barrier k
+constexpr int kStampPeerWait = 192;    // + s: nanoseconds block 0 waited for peers' flags before stage s
+constexpr int kStampTrace = 248;       // + point: role-level trace of one tile
+constexpr uint32_t kTrustCarried = 1u; // launch flag: state untouched since the previous launch of this module
+constexpr int kCarriedWord = 8;        // status word: values carried over from the previous launch are valid
+
 enum : uint32_t {
     kOk = 0,
     kErrGridBarrier = 1,
@@ -150,6 +158,8 @@ struct Ctx {
     Dp dp;
     uint32_t* sync;        // {count, generation} of this launch's barrier slot
     uint32_t* status;      // {code, stage, block, detail}
+    uint64_t* stamps;      // timestamp area when the kernel was generated with stage stamps, else null
+    uint32_t flags;        // launch flags (kTrustCarried)
     uint64_t timeout_ns;
     uint32_t arrivals;     // blocks the grid barrier waits for (gridDim.x unless a test overrides it)
     SharedState* sh;
@@ -198,6 +208,7 @@ __device__ __forceinline__ void ctx_init(Ctx& c, uint32_t* sync, uint32_t* statu
     c.arrivals = arrivals ? arrivals : gridDim.x;
     c.slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
     c.stage_id = 0; c.slot = 0; c.slot_phase = 0; c.acc = 0; c.acc_phase = 0; c.tmem = 0; c.epi = nullptr;
+    c.stamps = nullptr; c.flags = 0;
     c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         sh->abort = 0;
@@ -241,6 +252,13 @@ __device__ __forceinline__ void grid_barrier(Ctx& c) {
     if (c.arrivals > 1 && threadIdx.x == 0 && !c.aborted()) {
         uint32_t* count = c.sync;
         uint32_t* gen = c.sync + 1;
+        if (c.stamps != nullptr && c.stage_id < 64) {
+            // barrier stall evidence: when block 0 arrived, and when the last block did (the timer only
+            // grows, so the maximum left by earlier launches never wins)
+            const uint64_t now = global_timer_ns();
+            if (blockIdx.x == 0) c.stamps[kStampArrive + c.stage_id] = now;
+            atomicMax(reinterpret_cast<unsigned long long*>(c.stamps + kStampLast + c.stage_id), static_cast<unsigned long long>(now));
+        }
         const uint32_t my_gen = ld_relaxed_gpu(gen);
         const uint32_t arrived = atom_add_acq_rel_gpu(count, 1u);
         if (arrived == c.arrivals - 1) {
@@ -560,6 +578,8 @@ __device__ __forceinline__ void dp_signal(const Dp& d, const void* const* peers,
 // Called by all threads of a block: returns once every rank has passed grid barrier `barrier` of this epoch.
 // Thread j watches rank j's flag, so the (system-scope) polls of the ranks overlap.
 __device__ __forceinline__ void dp_wait(Ctx& c, const Dp& d, int world, int barrier) {
+    const bool stamped = c.stamps != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && c.stage_id < 56;
+    const uint64_t begun = stamped ? global_timer_ns() : 0;
     if (threadIdx.x < world && !c.aborted()) {
         const int j = threadIdx.x;
         const uint32_t* word = d.flags + 16 + j * 64 + barrier;
@@ -574,6 +594,7 @@ __device__ __forceinline__ void dp_wait(Ctx& c, const Dp& d, int world, int barr
         }
     }
     __syncthreads();
+    if (stamped) c.stamps[kStampPeerWait + c.stage_id] = global_timer_ns() - begun;
 }
 __device__ __forceinline__ void dp_finish(const Dp& d) { st_relaxed_gpu(d.flags, d.epoch); }
 
@@ -839,10 +860,10 @@ __device__ __forceinline__ void epilogue_chunk(Ctx& c, const Params& P, const fl
 // ----------------------------------------------------------------------------
 // Optional role-level timestamps of ONE stage's first tensor-core tile (compile with
 // -DTK_TRACE_STAGE=<stage>): the thread that reaches point k while working on tile 0 of that stage
-// writes the global timer to stamp slot 32 + k.  Points: 0 producer starts, 1 last TMA issued,
+// writes the global timer to stamp slot kStampTrace + k.  Points: 0 producer starts, 1 last TMA issued,
 // 2 first operands landed, 3 last MMA committed, 4 accumulator seen complete, 5 epilogue done.
 #ifdef TK_TRACE_STAGE
-#define TK_TRACE(point, tile) do { if (c.stage_id == TK_TRACE_STAGE && (tile) == 0) P.stamps[32 + (point)] = global_timer_ns(); } while (0)
+#define TK_TRACE(point, tile) do { if (c.stage_id == TK_TRACE_STAGE && (tile) == 0) P.stamps[tk::kStampTrace + (point)] = global_timer_ns(); } while (0)
 #else
 #define TK_TRACE(point, tile) do { } while (0)
 #endif

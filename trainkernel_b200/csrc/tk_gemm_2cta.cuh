@@ -51,6 +51,7 @@ __device__ __forceinline__ void ctx_init2(Ctx& c, uint32_t* sync, uint32_t* stat
     c.arrivals = arrivals ? arrivals : gridDim.x;
     c.slots = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn) + 1023) & ~uintptr_t(1023));
     c.stage_id = 0; c.slot = 0; c.slot_phase = 0; c.acc = 0; c.acc_phase = 0; c.tmem = 0; c.epi = nullptr;
+    c.stamps = nullptr; c.flags = 0;
     c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         sh->abort = 0;

@@ -9,7 +9,8 @@
 //
 // The workspace is the file-scope device array below: TK_STATIC_WORKSPACE_BYTES (4 MiB) per
 // device, reserved for as long as this library is loaded in a process that has touched that
-// device.  Kernels whose plan needs more are rejected.  Every call on a device uses the same
+// device.  Kernels whose plan needs more are rejected, and so is a `device` that is not the one the
+// module was loaded on (the address handed to the kernel would belong to another GPU's array).  Every call on a device uses the same
 // array, so two launches that can overlap on the GPU (different streams, or different modules)
 // race on it; order them on one stream.  The generated kernels write every workspace region
 // before reading it, so nothing has to be cleared between calls; whatever the previous call
@@ -48,6 +49,19 @@ extern "C" int tk_module_launch_static_workspace(tk_module* module, int device, 
     if (!module || device < 0 || device >= kMaxDevices)
         return report(error, error_capacity, TK_E_ARGUMENT, "trainkernel: invalid argument to %s (device %llu of at most %llu)",
                       "tk_module_launch_static_workspace", (unsigned long long)(device < 0 ? 0 : device), (unsigned long long)kMaxDevices);
+    // What the caller says must agree with what the module knows about itself: a wrong ordinal would hand
+    // the kernel the address of another GPU's copy of the array, an understated size would let it write
+    // past the end.
+    int loaded_on = -1;
+    size_t planned = 0;
+    if (tk_module_device(module, &loaded_on) || tk_module_workspace_bytes(module, &planned))
+        return report(error, error_capacity, TK_E_ARGUMENT, "trainkernel: %s: the module handle is not valid (%llu, %llu)",
+                      "tk_module_launch_static_workspace", 0ull, 0ull);
+    if (loaded_on != device)
+        return report(error, error_capacity, TK_E_ARGUMENT,
+                      "trainkernel: %s: the module was loaded on device %llu, not on device %llu",
+                      "tk_module_launch_static_workspace", (unsigned long long)loaded_on, (unsigned long long)device);
+    if (planned > workspace_bytes) workspace_bytes = planned;
     if (workspace_bytes > TK_STATIC_WORKSPACE_BYTES)
         return report(error, error_capacity, TK_E_CAPACITY,
                       "trainkernel: %s: the kernel needs %llu workspace bytes but the built-in workspace holds %llu; use tk_module_launch with a caller-owned buffer",
@@ -56,13 +70,15 @@ extern "C" int tk_module_launch_static_workspace(tk_module* module, int device, 
     {
         std::lock_guard<std::mutex> guard(g_mutex);
         if (!g_address[device]) {
-            int previous = 0;
+            // Make the module's device current for the lookup.  The previous device is put back only when
+            // it was a different one: selecting a device this process never used would create a context there.
+            int previous = device;
             cudaError_t status = cudaGetDevice(&previous);
-            if (status == cudaSuccess) status = cudaSetDevice(device);
+            if (status == cudaSuccess && previous != device) status = cudaSetDevice(device);
             void* address = nullptr;
             if (status == cudaSuccess) {
                 status = cudaGetSymbolAddress(&address, tk_static_workspace);
-                cudaSetDevice(previous);
+                if (previous != device) cudaSetDevice(previous);
             }
             if (status != cudaSuccess || !address)
                 return report(error, error_capacity, static_cast<int>(status ? status : cudaErrorUnknown),

@@ -35,7 +35,8 @@ int fail(int code, const char* format, ...) {
     X(cuModuleLoadData) X(cuModuleUnload) X(cuModuleGetFunction) X(cuFuncSetAttribute)              \
     X(cuFuncGetAttribute) X(cuOccupancyMaxActiveBlocksPerMultiprocessor) X(cuLaunchKernelEx)        \
     X(cuMemAlloc) X(cuMemFree) X(cuMemsetD8) X(cuMemcpyDtoH) X(cuStreamSynchronize)                 \
-    X(cuTensorMapEncodeTiled) X(cuGetErrorString) X(cuOccupancyMaxActiveClusters)
+    X(cuTensorMapEncodeTiled) X(cuGetErrorString) X(cuOccupancyMaxActiveClusters)                   \
+    X(cuStreamGetCaptureInfo) X(cuMemsetD32Async)
 
 struct Driver {
 #define X(sym) decltype(&sym) sym##_ = nullptr;
@@ -83,7 +84,9 @@ int check(CUresult result, const char* what) {
 
 constexpr int kSyncSlots = 64;        // one {count, generation} pair per 128-byte line
 constexpr int kSyncStride = 128;
-constexpr int kStampCount = 64;
+constexpr int kStampCount = 256;     // stage stamps | block 0's barrier arrivals | latest arrivals | peer waits + role trace
+constexpr int kMapWays = 4;           // encoded tensor maps remembered per map slot
+constexpr int kCarriedWord = 8;       // status word that says "values carried over from the previous launch are valid"
 
 struct ContextScope {
     bool pushed = false;
@@ -114,13 +117,19 @@ struct tk_module {
     int blocks_per_sm = 0;
     int cluster = 1;
     std::atomic<int> cooperative{1};
-    // Encoded tensor maps of the last launch, keyed by their base address: a caller that launches with the
-    // same buffers again (the common case in an eager loop) does not pay for re-encoding them.
+    // Encoded tensor maps of recent launches, kMapWays per map slot keyed by base address: a caller that
+    // cycles through a few resident batches or double buffers (the common case in an eager loop) does not
+    // pay for re-encoding them.
     std::mutex map_mutex;
-    std::vector<const void*> map_base;
+    std::vector<const void*> map_base;       // [slot * kMapWays + way]
     std::vector<CUtensorMap> map_cache;
+    std::vector<uint8_t> map_next;           // way to replace next, per slot
     int max_blocks = 0;               // co-resident capacity for the current cluster size
     size_t param_bytes = 0;
+    int ordinal = 0;                  // device ordinal the module was loaded on
+    std::atomic<size_t> workspace_bytes{0};  // what the kernel's plan needs (0: not recorded)
+    std::atomic<int> faulted{0};      // tk_module_status saw an error; launches are refused until tk_module_reset
+    std::atomic<unsigned long long> capture_id{0};   // last stream capture a launch was recorded into
 
     CUdeviceptr sync_slot(uint32_t i) const { return state + static_cast<size_t>(i) * kSyncStride; }
     CUdeviceptr status() const { return state + static_cast<size_t>(kSyncSlots) * kSyncStride; }
@@ -143,6 +152,7 @@ int tk_module_load(const void* cubin, size_t cubin_bytes, const char* entry, int
     if (int rc = driver()) return rc;
     tk_module* m = new tk_module();
     m->threads = threads;
+    m->ordinal = device;
     m->dynamic_smem = dynamic_smem;
     m->n_inputs = n_inputs;
     m->n_outputs = n_outputs;
@@ -196,13 +206,20 @@ void tk_module_unload(tk_module* m) {
 }
 
 int tk_module_launch(tk_module* m, const void* const* inputs, void* const* outputs, void* workspace, int grid, void* stream) {
+    return tk_module_launch_flags(m, inputs, outputs, workspace, grid, stream, 0u);
+}
+
+int tk_module_launch_flags(tk_module* m, const void* const* inputs, void* const* outputs, void* workspace, int grid, void* stream,
+                           uint32_t flags) {
     if (!m || grid < 1 || (m->n_inputs > 0 && !inputs) || (m->n_outputs > 0 && !outputs))
         return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_launch");
+    if (m->faulted.load())
+        return fail(TK_E_KERNEL, "trainkernel: an earlier launch of this kernel reported a timed-out wait; call tk_module_reset before launching again");
     if (grid > m->max_blocks || grid % m->cluster)
         return fail(TK_E_CAPACITY, "trainkernel: grid %d exceeds the %d co-resident blocks a cooperative launch allows (cluster size %d)", grid,
                     m->max_blocks, m->cluster);
     // Kernel parameter block: tensor maps, input pointers, output pointers, then the scalars.
-    alignas(64) unsigned char block[4096];
+    alignas(64) unsigned char block[8192];
     if (m->param_bytes > sizeof(block)) return fail(TK_E_ARGUMENT, "trainkernel: parameter block too large");
     memset(block, 0, m->param_bytes);
     for (size_t i = 0; i < m->maps.size(); ++i) {
@@ -216,23 +233,30 @@ int tk_module_launch(tk_module* m, const void* const* inputs, void* const* outpu
         if (reinterpret_cast<uintptr_t>(base) & 15)
             return fail(TK_E_ARGUMENT, "trainkernel: tensor-core operand %zu is not 16-byte aligned", i);
         std::lock_guard<std::mutex> guard(m->map_mutex);
-        if (m->map_base.size() != m->maps.size()) {
-            m->map_base.assign(m->maps.size(), nullptr);
-            m->map_cache.resize(m->maps.size());
+        if (m->map_base.size() != m->maps.size() * kMapWays) {
+            m->map_base.assign(m->maps.size() * kMapWays, nullptr);
+            m->map_cache.resize(m->maps.size() * kMapWays);
+            m->map_next.assign(m->maps.size(), 0);
         }
-        if (m->map_base[i] != base) {
+        int way = -1;
+        for (int w = 0; w < kMapWays; ++w)
+            if (m->map_base[i * kMapWays + w] == base) { way = w; break; }
+        if (way < 0) {
+            way = m->map_next[i];
+            m->map_next[i] = static_cast<uint8_t>((way + 1) % kMapWays);
             cuuint64_t dims[2] = {d.inner, d.outer};
             cuuint64_t strides[1] = {d.outer_stride_bytes};
             cuuint32_t box[2] = {d.box_inner, d.box_outer};
             cuuint32_t element_strides[2] = {1, 1};
+            m->map_base[i * kMapWays + way] = nullptr;
             CUresult result = g_driver.cuTensorMapEncodeTiled_(
-                &m->map_cache[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                &m->map_cache[i * kMapWays + way], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                 const_cast<unsigned char*>(base), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (int rc = check(result, "cuTensorMapEncodeTiled")) { m->map_base[i] = nullptr; return rc; }
-            m->map_base[i] = base;
+            if (int rc = check(result, "cuTensorMapEncodeTiled")) return rc;
+            m->map_base[i * kMapWays + way] = base;
         }
-        memcpy(block + 128 * i, &m->map_cache[i], sizeof(CUtensorMap));
+        memcpy(block + 128 * i, &m->map_cache[i * kMapWays + way], sizeof(CUtensorMap));
     }
     unsigned char* cursor = block + 128 * static_cast<size_t>(m->slots_maps);
     for (int i = 0; i < m->n_inputs; ++i) memcpy(cursor + 8 * i, &inputs[i], 8);
@@ -251,6 +275,18 @@ int tk_module_launch(tk_module* m, const void* const* inputs, void* const* outpu
     memcpy(cursor + 40, &arrivals, 4);
 
     ContextScope scope(m->context);
+    // Values carried over from the previous launch are trusted only on the caller's word, and never by the
+    // first launch recorded into a stream capture: a replayed graph starts from whatever the caller left.
+    if (flags & TK_LAUNCH_TRUST_CARRIED) {
+        CUstreamCaptureStatus capture = CU_STREAM_CAPTURE_STATUS_NONE;
+        cuuint64_t id = 0;
+        if (g_driver.cuStreamGetCaptureInfo_(static_cast<CUstream>(stream), &capture, &id, nullptr, nullptr, nullptr) != CUDA_SUCCESS)
+            flags &= ~TK_LAUNCH_TRUST_CARRIED;
+        else if (capture == CU_STREAM_CAPTURE_STATUS_ACTIVE && m->capture_id.exchange(id) != id)
+            flags &= ~TK_LAUNCH_TRUST_CARRIED;
+    }
+    memcpy(cursor + 44, &flags, 4);
+
     CUlaunchAttribute attribute[2];
     memset(attribute, 0, sizeof(attribute));
     unsigned attributes = 0;
@@ -342,6 +378,7 @@ int tk_module_status(tk_module* m, void* stream, uint32_t out[4]) {
     ContextScope scope(m->context);
     if (int rc = check(g_driver.cuStreamSynchronize_(static_cast<CUstream>(stream)), "cuStreamSynchronize")) return rc;
     if (int rc = check(g_driver.cuMemcpyDtoH_(out, m->status(), 16), "cuMemcpyDtoH(status)")) return rc;
+    if (out[0] != 0) m->faulted.store(1);
     if (out[0] != 0)
         return fail(TK_E_KERNEL, "trainkernel: kernel wait timed out (code %u, stage %u, block %u, detail %u)", out[0], out[1], out[2], out[3]);
     return 0;
@@ -351,7 +388,33 @@ int tk_module_reset(tk_module* m) {
     if (!m) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_reset");
     ContextScope scope(m->context);
     if (int rc = check(g_driver.cuCtxSynchronize_(), "cuCtxSynchronize")) return rc;
-    return check(g_driver.cuMemsetD8_(m->state, 0, m->state_bytes()), "cuMemsetD8(kernel state)");
+    if (int rc = check(g_driver.cuMemsetD8_(m->state, 0, m->state_bytes()), "cuMemsetD8(kernel state)")) return rc;
+    m->faulted.store(0);
+    return 0;
+}
+
+int tk_module_device(tk_module* m, int* out) {
+    if (!m || !out) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_device");
+    *out = m->ordinal;
+    return 0;
+}
+
+int tk_module_set_workspace_bytes(tk_module* m, size_t bytes) {
+    if (!m) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_set_workspace_bytes");
+    m->workspace_bytes.store(bytes);
+    return 0;
+}
+
+int tk_module_workspace_bytes(tk_module* m, size_t* out) {
+    if (!m || !out) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_workspace_bytes");
+    *out = m->workspace_bytes.load();
+    return 0;
+}
+
+int tk_module_invalidate_carried(tk_module* m, void* stream) {
+    if (!m) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_invalidate_carried");
+    ContextScope scope(m->context);
+    return check(g_driver.cuMemsetD32Async_(m->status() + 4 * kCarriedWord, 0u, 1, static_cast<CUstream>(stream)), "cuMemsetD32Async(carried word)");
 }
 
 int tk_module_set_timeout(tk_module* m, uint64_t nanoseconds) {

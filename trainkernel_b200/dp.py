@@ -29,6 +29,64 @@ from .frontend import capture
 from .passes import split_at_gradients
 
 
+class PeerFailure(RuntimeError):
+    """A peer rank reported a failure, or gave no sign of life within the limit."""
+
+    def __init__(self, rank: int, reason: str) -> None:
+        super().__init__(f"trainkernel: rank {rank} failed: {reason}")
+        self.rank = rank
+        self.reason = reason
+
+
+class PeerHealth:
+    """Host-side liveness of the ranks of a sharded step, kept in a `torch.distributed` key-value store.
+
+    The step kernels of all ranks wait for each other's flags on the device (bounded, two seconds by
+    default, after which the launch is lost and every rank has to reset).  It is cheaper to learn on the
+    HOST that a peer is gone and not launch at all: every rank calls `arrive(step)` when it is about to
+    launch step `step`, and `wait_for_peers(step)` returns once every rank has arrived at that step, or
+    raises `PeerFailure` naming the rank that reported a failure (`report_failure`, typically from an
+    `except` block) or that stayed silent for `timeout_s`.  Nothing here touches a GPU.
+    """
+
+    def __init__(self, store, rank: int, world: int, *, timeout_s: float = 5.0, prefix: str = "trainkernel/health") -> None:
+        self.store, self.rank, self.world = store, rank, world
+        self.timeout_s, self.prefix = timeout_s, prefix
+
+    def arrive(self, step: int) -> None:
+        self.store.set(f"{self.prefix}/step/{self.rank}", str(int(step)))
+
+    def report_failure(self, reason: str) -> None:
+        self.store.set(f"{self.prefix}/failed/{self.rank}", str(reason) or "unspecified")
+
+    def failed_peer(self) -> tuple[int, str] | None:
+        for peer in range(self.world):
+            key = f"{self.prefix}/failed/{peer}"
+            if peer != self.rank and self.store.check([key]):
+                return peer, self.store.get(key).decode()
+        return None
+
+    def wait_for_peers(self, step: int) -> None:
+        import time
+        deadline = time.monotonic() + self.timeout_s
+        waiting = [peer for peer in range(self.world) if peer != self.rank]
+        while True:
+            failed = self.failed_peer()
+            if failed is not None:
+                raise PeerFailure(*failed)
+            still = []
+            for peer in waiting:
+                key = f"{self.prefix}/step/{peer}"
+                if not self.store.check([key]) or int(self.store.get(key).decode()) < step:
+                    still.append(peer)
+            waiting = still
+            if not waiting:
+                return
+            if time.monotonic() > deadline:
+                raise PeerFailure(waiting[0], f"no sign of life for {self.timeout_s:g} s while waiting for step {step}")
+            time.sleep(0.002)
+
+
 def shard_rows(batch: int, rank: int, world: int) -> slice:
     """Rows of the global batch owned by `rank`; the batch must divide evenly."""
     if batch % world:
@@ -131,6 +189,12 @@ class ShardedTrainingStep:
         self.gradient.status()
         self.update.status()
 
+    def close(self) -> None:
+        """Wait for this rank's work and drop the kernels and buffers (call before the process group goes away)."""
+        torch.cuda.synchronize(self.device)
+        self.gradient = self.update = None
+        self.flat = self.views = self.gradients = None
+
 
 def spec_numel(shape: tuple[int, ...]) -> int:
     total = 1
@@ -175,8 +239,11 @@ class FusedShardedTrainingStep:
     MULTICAST_FROM = 4
 
     def __init__(self, fn: Callable[..., Any], example_inputs: Sequence[Any], *, group: Any = None,
-                 multicast: bool | None = None, **options: Any) -> None:
+                 multicast: bool | None = None, health: PeerHealth | None = None, **options: Any) -> None:
         from .codegen import generate
+        self.group = group
+        self.health = health
+        self.steps_launched = 0
         from .passes import insert_gradient_exchange
         if "inplace_outputs" in options or "world" in options:
             raise ValueError("trainkernel: the sharded step derives its own state mapping and world size")
@@ -250,6 +317,11 @@ class FusedShardedTrainingStep:
             raise ValueError("trainkernel: runtime input pytree differs from the compiled signature")
         flat = tuple(flat)
         self._checker._validate_inputs(flat)
+        if self.health is not None and not torch.cuda.is_current_stream_capturing():
+            # learn on the host that a peer is gone instead of launching a kernel that would wait for it
+            self.health.arrive(self.steps_launched)
+            self.health.wait_for_peers(self.steps_launched)
+        self.steps_launched += 1
         state = flat[:self.count]
         stream = torch.cuda.current_stream(self.device).cuda_stream
         self.module.launch((*flat, *self._extra), (self.loss, *self.gradients, *state), self.workspace, stream)
@@ -258,3 +330,47 @@ class FusedShardedTrainingStep:
 
     def status(self) -> None:
         self._checker.status()
+
+    def check(self) -> None:
+        """Collective status check: every rank synchronises, the ranks agree on whether ANY of them saw a
+        timed-out wait, and if so ALL of them reset (kernel status words, barrier words, the epoch and flag
+        words of the peer-mapped header) before `RuntimeError` is raised on every rank.  A kernel that
+        gave up leaves partial outputs and an epoch that differs from its peers', so one rank cannot
+        recover alone.  Call it every few steps of a long loop; it costs a device synchronisation."""
+        message = ""
+        try:
+            self._checker.status()
+        except RuntimeError as error:
+            message = str(error)
+        failed = torch.tensor([1 if message else 0], dtype=torch.int32, device=self.device)
+        if self.world > 1:
+            dist.all_reduce(failed, op=dist.ReduceOp.MAX, group=self.group)
+        if not int(failed.item()):
+            return
+        self.recover()
+        raise RuntimeError(message or "trainkernel: a peer rank's step kernel reported a timed-out wait; all ranks were reset")
+
+    def recover(self) -> None:
+        """Reset this rank's kernel state and exchange header; every rank must call it at the same point."""
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(self.group)
+        self.module.lib.tk_module_reset(self.module.handle)
+        header = self.symmetric[:1024]
+        header.zero_()
+        self.symmetric[1] = self.rank
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(self.group)
+
+    def close(self) -> None:
+        """Wait for this rank's work, then release the kernel, the rendezvous handle and the peer-mapped
+        buffer, in that order.  Every rank should call it (followed by a barrier) before the process
+        group is destroyed or the process exits, so that no rank's memory disappears while a peer still
+        has it mapped or bound to the switch's multicast object."""
+        torch.cuda.synchronize(self.device)
+        self.module = None
+        self._checker = None
+        self._extra = []
+        self._handle = None
+        self.symmetric = None

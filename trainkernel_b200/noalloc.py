@@ -59,6 +59,10 @@ def launch_static_workspace(runner: runtime.CompiledProgram, inputs, outputs) ->
     Raises when the kernel needs more than `STATIC_WORKSPACE_BYTES` of workspace.
     """
     module = runner.module
+    inputs, outputs = tuple(inputs), tuple(outputs)
+    # the same argument checks as every other launch path; none of them allocates
+    runner._validate_inputs(inputs)
+    runner._check_outputs(inputs, outputs)
     ins = (ctypes.c_void_p * module.n_in)(*[t.data_ptr() for t in inputs])
     outs = (ctypes.c_void_p * module.n_out)(*[t.data_ptr() for t in outputs])
     message = ctypes.create_string_buffer(512)

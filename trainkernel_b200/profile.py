@@ -20,7 +20,10 @@ def stage_profile(fn: Callable[..., Any], example_inputs: Sequence[Any], *, trai
     """Compile `fn` with stage stamps, run it `repeats` times, and return one record per stage.
 
     Each record holds the stage index, the fastest and median duration in microseconds (a stage's
-    time includes the grid barrier that ends it, as seen by block 0), and the units scheduled in it.
+    time includes the grid barrier that ends it, as seen by block 0), the units scheduled in it and,
+    for every stage that ends in a grid barrier, the barrier's stall times (medians, microseconds):
+    `barrier_wait_us` block 0's arrival to its release, `barrier_skew_us` block 0's arrival to the
+    last block's arrival, `barrier_release_us` last arrival to release (the cost of the barrier itself).
     State tensors in `example_inputs` are updated by the runs when `training` is true.
     """
     builder = compile_training if training else compile
@@ -30,15 +33,22 @@ def stage_profile(fn: Callable[..., Any], example_inputs: Sequence[Any], *, trai
         compiled(*example_inputs)
     torch.cuda.synchronize(runner.device)
     samples: list[list[float]] = []
+    stalls: list[list[dict]] = []
     for _ in range(repeats):
         compiled(*example_inputs)
         stamps = runner.stage_stamps()
         samples.append([(b - a) / 1e3 for a, b in zip(stamps[:-1], stamps[1:])])
+        stalls.append(runner.barrier_stalls())
     records = []
     for stage in range(runner.generated.stages):
         column = sorted(sample[stage] for sample in samples)
         units = [f"{name}:{kind}{'/' + path if path else ''}" for s, kind, name, path, _ in runner.generated.units if s == stage]
-        records.append({"stage": stage, "min_us": column[0], "median_us": column[len(column) // 2], "units": units})
+        record = {"stage": stage, "min_us": column[0], "median_us": column[len(column) // 2], "units": units}
+        if stalls and stage < len(stalls[0]):
+            for key, label in (("block0_wait", "barrier_wait_us"), ("skew", "barrier_skew_us"), ("release", "barrier_release_us")):
+                values = sorted(run[stage][key] / 1e3 for run in stalls)
+                record[label] = values[len(values) // 2]
+        records.append(record)
     return records
 
 
@@ -76,9 +86,9 @@ def main(argv=None) -> int:
         best = None
         for _ in range(3 + args.repeats):
             compiled(*inputs)
-            stamps = compiled.runner.stage_stamps(38)
+            stamps = compiled.runner.stage_stamps()
             start = stamps[args.trace_stage]
-            points = [(value - start) / 1e3 for value in stamps[32:38]] + [(stamps[args.trace_stage + 1] - start) / 1e3]
+            points = [(value - start) / 1e3 for value in compiled.runner.role_trace()] + [(stamps[args.trace_stage + 1] - start) / 1e3]
             if best is None or points[-1] < best[-1]:
                 best = points
         names = ("producer_starts", "last_tma_issued", "first_operands_landed", "last_mma_committed",

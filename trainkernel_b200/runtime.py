@@ -90,6 +90,11 @@ def library() -> ctypes.CDLL:
         lib.tk_module_load.argtypes = [p, ctypes.c_size_t, ctypes.c_char_p, i32, i32, ctypes.c_size_t, i32, i32,
                                        ctypes.POINTER(TensorMapDesc), i32, ctypes.POINTER(p)]
         lib.tk_module_launch.argtypes = [p, ctypes.POINTER(p), ctypes.POINTER(p), p, i32, p]
+        lib.tk_module_launch_flags.argtypes = [p, ctypes.POINTER(p), ctypes.POINTER(p), p, i32, p, u32]
+        lib.tk_module_invalidate_carried.argtypes = [p, p]
+        lib.tk_module_device.argtypes = [p, ctypes.POINTER(i32)]
+        lib.tk_module_set_workspace_bytes.argtypes = [p, ctypes.c_size_t]
+        lib.tk_module_workspace_bytes.argtypes = [p, ctypes.POINTER(ctypes.c_size_t)]
         lib.tk_module_resource_usage.argtypes = [p, ctypes.POINTER(ctypes.c_int64)]
         lib.tk_module_max_coresident_blocks.argtypes = [p, ctypes.POINTER(i32)]
         lib.tk_module_status.argtypes = [p, p, ctypes.POINTER(u32)]
@@ -178,6 +183,7 @@ class _Module:
             _raise(code)
         self.handle = handle
         self.lib = lib
+        lib.tk_module_set_workspace_bytes(handle, generated.workspace_bytes)
         if generated.cluster > 1:
             code = lib.tk_module_set_cluster(handle, generated.cluster)
             if code:
@@ -251,15 +257,34 @@ class CompiledProgram:
             _raise(code)
         return tuple(int(w) for w in words)
 
-    def stage_stamps(self, count: int | None = None) -> list[int]:
-        """Per-stage %globaltimer values of the last launch (kernel generated with `stage_stamps=True`)."""
-        count = self.generated.stages + 1 if count is None else count
+    def _stamps(self, count: int) -> list[int]:
         stamps = (ctypes.c_uint64 * count)()
         stream = torch.cuda.current_stream(self.device).cuda_stream
         code = self.module.lib.tk_module_stage_stamps(self.module.handle, stream, stamps, count)
         if code:
             _raise(code)
         return [int(s) for s in stamps]
+
+    def stage_stamps(self, count: int | None = None) -> list[int]:
+        """Per-stage %globaltimer values of the last launch (kernel generated with `stage_stamps=True`)."""
+        return self._stamps(self.generated.stages + 1 if count is None else count)
+
+    def barrier_stalls(self) -> list[dict]:
+        """Per grid barrier of the last launch (kernel generated with `stage_stamps=True`), nanoseconds:
+        `block0_wait` from block 0's arrival to its release, `skew` from block 0's arrival to the last
+        block's arrival (negative when block 0 was last), `release` from the last arrival to the release,
+        and `peer_wait`, what block 0 then spent waiting for other ranks' flags before the next stage."""
+        words = self._stamps(256)
+        records = []
+        for barrier in range(self.generated.grid_barriers if self.generated.barrier == "grid" else 0):
+            arrive, last, release = words[64 + barrier], words[128 + barrier], words[barrier + 1]
+            records.append({"barrier": barrier, "block0_wait": release - arrive, "skew": last - arrive,
+                            "release": release - last, "peer_wait": words[192 + barrier + 1] if self.generated.world > 1 else 0})
+        return records
+
+    def role_trace(self) -> list[int]:
+        """The six role-level %globaltimer values of the traced tile (kernel generated with `trace_stage=`)."""
+        return self._stamps(256)[248:254]
 
     # -- argument checks -------------------------------------------------------------
     def _validate_inputs(self, inputs: tuple[torch.Tensor, ...]) -> None:
@@ -296,11 +321,17 @@ class CompiledProgram:
 
     def _check_buffers(self, inputs: tuple[torch.Tensor, ...], buffers: ExecutionBuffers) -> None:
         outputs, workspace = buffers.outputs, buffers.workspace
-        if len(outputs) != len(self.program.outputs):
-            raise ValueError("trainkernel: incorrect output buffer count")
         if (workspace.device != self.device or workspace.dtype != torch.float32 or not workspace.is_contiguous()
                 or workspace.numel() < self.generated.workspace_elements):
             raise ValueError("trainkernel: workspace does not match compiled requirements")
+        self._check_outputs(inputs, outputs, workspace)
+
+    def _check_outputs(self, inputs: tuple[torch.Tensor, ...], outputs: tuple[torch.Tensor, ...],
+                       workspace: torch.Tensor | None = None) -> None:
+        """Output count, shape, dtype and layout; in-place slots bound to their inputs; nothing written
+        shares storage with anything else that is read or written.  Allocates nothing."""
+        if len(outputs) != len(self.program.outputs):
+            raise ValueError("trainkernel: incorrect output buffer count")
         # Storage-level disjointness: conservative, but a write can then never clobber something still to be read.
         written: list[int] = []
         shared_with_inputs: set[int] = set()
@@ -323,7 +354,7 @@ class CompiledProgram:
                     if other != index and value.numel() and value.untyped_storage().data_ptr() == storage:
                         raise ValueError("trainkernel: inplace target must not alias another input")
                 shared_with_inputs.add(storage)
-        if workspace.numel():
+        if workspace is not None and workspace.numel():
             written.append(workspace.untyped_storage().data_ptr())
         read = {tensor.untyped_storage().data_ptr() for tensor in inputs if tensor.numel()}
         if len(set(written)) != len(written) or (read & set(written)) - shared_with_inputs:
