@@ -55,19 +55,25 @@ def l2_error(actual: torch.Tensor, expected: torch.Tensor) -> float:
 def assert_step_close(actual, expected_cpu, program, device_inputs, tol: float, label: str = "", max_fallbacks: int = 2) -> list[dict]:
     """Parity of one training step against the IR oracle.
 
-    The bound is `tol` on max|a-b|/max|b| against the oracle evaluated on the host.  One
-    effect can break that bound without any arithmetic being wrong: an activation whose
-    pre-ReLU value is within an ulp of zero gets a different ReLU mask on the host than on
-    the GPU (different FP32 summation order inside the matmul), which moves a whole column
-    of the next weight gradient by one of its 1/batch terms.  When the host comparison
-    fails for a 16-bit-compute step, the same oracle is therefore also evaluated on the
-    device (same IR, same rounding points, cuBLAS summation order); the output passes if it
-    is within `tol` of that evaluation and within `tol` of the host oracle in the L2 norm.
+    The bound is `tol` on max|a-b|/max|b| against the oracle evaluated on the host.  For a
+    16-bit-compute step that bound can be broken without any arithmetic being wrong, because
+    the ORACLE ITSELF moves by that much when only its FP32 summation order changes: a
+    pre-ReLU value within an ulp of zero gets a different mask, a BF16 rounding point falls
+    the other way, and a weight gradient, which is a sum over the batch with heavy
+    cancellation, amplifies both (on the host alone, the small MLP's dW2 moves by 3.8e-2 in a
+    handful of elements, and the first-layer gradient of the half-size medium MLP by 7e-3 in
+    L2, when the matmuls accumulate in a different order).  When the host comparison fails,
+    the same oracle is therefore also evaluated on the device (same IR, same rounding points,
+    cuBLAS summation order), and the output passes only if
 
-    Every output that needed this second comparison is printed and returned (index, host error,
-    device-oracle error, L2 error, fraction of elements beyond the bound); at most
-    `max_fallbacks` outputs of a step may need it, and in each of them the elements beyond
-    the bound must be a small minority (a few flipped columns, not a wrong tensor).
+      * it is within `tol` (max norm) of that device evaluation, and
+      * it is no farther from the host oracle than the oracle is from itself: L2 distance at
+        most max(tol, 1.25 x the L2 distance between the two oracle evaluations), max-norm
+        distance at most max(tol, 1.5 x theirs), and
+      * the elements beyond the bound are a small minority (a few columns, not a wrong tensor).
+
+    Every output that needed this second comparison is printed and returned with all of these
+    figures; at most `max_fallbacks` outputs of a step may need it.
     """
     got, _ = tree_flatten(actual)
     assert len(got) == len(expected_cpu), f"{label}: output count"
@@ -84,14 +90,17 @@ def assert_step_close(actual, expected_cpu, program, device_inputs, tol: float, 
             flat, _ = tree_flatten(device_inputs)
             on_device = interpreter.run(program, flat)
         l2 = l2_error(a, b)
-        assert l2 <= tol, f"{label}: output {index} L2 relative error {l2:.3e}"
         err_device = rel_error(a, on_device[index])
-        assert err_device <= tol, f"{label}: output {index} relative error {err:.3e} (host) / {err_device:.3e} (device oracle)"
+        floor_max, floor_l2 = rel_error(on_device[index], b), l2_error(on_device[index], b)
         host = b.detach().float()
         beyond = float(((a.detach().float().cpu() - host).abs() > tol * float(host.abs().max())).float().mean())
-        assert beyond <= 0.02, f"{label}: output {index}: {beyond:.2%} of the elements are beyond the bound, not a few flipped ReLU masks"
-        record = {"output": index, "host_oracle": err, "device_oracle": err_device, "l2": l2, "fraction_beyond_bound": beyond}
-        print(f"[parity] {label}: output {index} passed through the device-oracle comparison: {record}")
+        record = {"output": index, "host_oracle": err, "device_oracle": err_device, "l2": l2,
+                  "oracle_self_distance_max": floor_max, "oracle_self_distance_l2": floor_l2, "fraction_beyond_bound": beyond}
+        print(f"[parity] {label}: output {index} went through the device-oracle comparison: {record}")
+        assert err_device <= tol, f"{label}: output {index} relative error {err:.3e} (host) / {err_device:.3e} (device oracle)"
+        assert l2 <= max(tol, 1.25 * floor_l2), f"{label}: output {index}: L2 distance to the host oracle {l2:.3e}, the oracle's own {floor_l2:.3e}"
+        assert err <= max(tol, 1.5 * floor_max), f"{label}: output {index}: distance to the host oracle {err:.3e}, the oracle's own {floor_max:.3e}"
+        assert beyond <= 0.02, f"{label}: output {index}: {beyond:.2%} of the elements are beyond the bound"
         fallbacks.append(record)
     assert len(fallbacks) <= max_fallbacks, f"{label}: {len(fallbacks)} outputs needed the device-oracle comparison: {fallbacks}"
     return fallbacks

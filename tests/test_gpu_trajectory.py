@@ -168,7 +168,7 @@ def test_medium_mlp_steps_and_graph_replay_match_the_oracle():
             assert bool(torch.isfinite(got.float()).all())
             assert rel_error(got, want) <= tol, f"step {step}, output {index}: {rel_error(got, want):.3e} from the device oracle"
         if step == 0:
-            assert_step_close(out, host_out, program, pristine, tol, "c5 step 0 against the host oracle")
+            assert_step_close(out, host_out, program, pristine, tol, "c5 step 0 against the host oracle", max_fallbacks=4)
     # 20-step graph replay from the initial state
     for p, saved in zip(state, initial):
         p.copy_(saved)
