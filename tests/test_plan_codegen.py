@@ -231,3 +231,49 @@ def test_fixed_size_stage_tables_are_guarded():
     with pytest.raises(ValueError, match="trace_stage needs"):
         generate(small, inplace_outputs=small_inplace, stage_stamps=True, trace_stage=99)
     assert generate(small, inplace_outputs=small_inplace, stage_stamps=True, trace_stage=1).stages <= codegen.MAX_STAMPED_STAGES
+
+
+def _medium_program(batch=8192):
+    sizes = (4096, 8192, 8192, 8192, 4096)
+    state = []
+    for fan_in, fan_out in zip(sizes[:-1], sizes[1:]):
+        state += [torch.empty(fan_in, fan_out, device="meta"), torch.empty(fan_out, device="meta")]
+    x = torch.empty(batch, sizes[0], dtype=torch.bfloat16, device="meta")
+    t = torch.empty(batch, sizes[-1], dtype=torch.bfloat16, device="meta")
+    program, _ = tk.capture(lambda s, xx, tt: workloads.mlp_master_step(s, xx, tt, 1e-3), (tuple(state), x, t))
+    return program, {1 + 8 + i: i for i in range(8)}
+
+
+def test_loss_and_bias_gradient_sums_are_formed_in_gemm_epilogues():
+    """In the BF16 configurations no reduce unit reads a [batch, out] tensor back from memory: the loss terms
+    and dY are summed per 32-row chunk in the epilogue of the GEMM that produces them, and the reduce units
+    only finish over those partial sums (reference stage replaced: trainkernel/codegen.py:443-504)."""
+    programs = {name: _step_program(name) for name in ("c2", "c3", "c4")}
+    programs["c5"] = _medium_program()
+    for name, (program, inplace) in programs.items():
+        plan = plan_program(program, inplace_outputs=inplace)
+        reduces = [u for u in plan.units if u.kind == "reduce"]
+        assert reduces, name
+        for unit in reduces:
+            # partial sums, plus at most the bias vector its fused SGD update reads
+            assert any(buffer.endswith("__partials") for buffer in unit.reads), (name, unit.name, unit.reads)
+            assert all(buffer.endswith("__partials") or len(plan.shapes[buffer]) <= 1 for buffer in unit.reads), (name, unit.name, unit.reads)
+            assert unit.phase in ("finish", "") and unit.phase != "partial"
+        hosts = [u for u in plan.units if u.kind == "gemm" and u.fused]
+        assert sum(len(u.fused) for u in hosts) == len(reduces)
+        for host in hosts:
+            for fused in host.fused:
+                m, n = host.dims
+                expected = -(-m // 32) * (1 if fused.mode == "cols" else -(-n // 32))
+                assert fused.parts == expected and plan.shapes[fused.scratch][0] == expected
+                assert plan.storage[fused.scratch][0] == "ws"
+    # the squared residual is no longer stored at all: only its partial sums leave the forward epilogue
+    program, inplace = programs["c5"]
+    plan = plan_program(program, inplace_outputs=inplace)
+    stored = {s.buffer for u in plan.units for s in u.stores}
+    assert not any(name.startswith("pow") for name in stored)
+    generated = generate(program, inplace_outputs=inplace)
+    assert "__shfl_xor_sync" in generated.source and "mean__partials" in generated.source
+    # without epilogue fusion the reductions read their operands from memory again
+    unfused = plan_program(program, inplace_outputs=inplace, fuse_epilogues=False)
+    assert any(u.kind == "reduce" and u.phase == "partial" for u in unfused.units)

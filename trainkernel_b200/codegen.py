@@ -270,8 +270,9 @@ class _Emitter:
             buffer = member.output.buffer
             env["ref:" + buffer] = self.value(unit.exprs[buffer], body, env, width, coords, nvalid)
         dense = row_major(unit.dims)
+        partials = {f.scratch for f in unit.fused}
         for store in unit.stores:
-            if unit.phase == "partial":
+            if unit.phase == "partial" or store.buffer in partials:
                 continue
             address = self._affine(0, dense, coords, False)
             where = self.plan.storage[store.buffer]
@@ -320,8 +321,11 @@ class _Emitter:
         body.emit(f"{self._loop('W')} {root}[r][j] = {rounding}::rnd({combine});")
         env["ref:" + op.output.buffer] = root
         self.dag(unit, body, env, "W", coords, "nv[r]")
+        for fused in unit.fused:
+            self._fused_reduce(unit, fused, body, env)
         self.rows = False
-        wide = any(ELEMENT_BYTES[s.dtype] == 4 for s in unit.stores)
+        partials = {f.scratch for f in unit.fused}
+        wide = any(ELEMENT_BYTES[s.dtype] == 4 for s in unit.stores if s.buffer not in partials)
         # tile-shaped operands the epilogue reads (same row/column as the accumulator): worth prefetching into L2
         fetched: list[Access] = []
 
@@ -354,6 +358,32 @@ class _Emitter:
             f"{prefetch}"
             f"    }}\n}};\n")
         return name
+
+    def _fused_reduce(self, unit: Unit, fused, body: _Body, env: dict) -> None:
+        """Partial sums of a member value over the 32 x 32 accumulator chunk a warp's epilogue call covers.
+
+        Inside `run_rows<R, W>` the 32 lanes of the warp hold the chunk as R runs of W columns each: lanes that
+        differ only above bit log2(32 / W) hold the same columns of different rows.  Rows at or beyond M and
+        columns at or beyond the run's valid count are left out.  The butterfly adds in a fixed order, so the
+        partials, and the finish over them, are deterministic.
+        """
+        m, n = unit.dims
+        value = env["ref:" + fused.buffer]
+        scratch = self.pointer(fused.scratch, "float32", False)
+        body.emit(f"// partial sums of {fused.buffer} for {fused.scratch} ({fused.mode})")
+        if fused.mode == "cols":
+            name = body.temp("cs")
+            body.emit(f"float {name}[W];")
+            body.emit(f"_Pragma(\"unroll\") for (int j = 0; j < W; ++j) {{ {name}[j] = 0.0f; _Pragma(\"unroll\") for (int r = 0; r < R; ++r) {name}[j] += (j < nv[r]) ? {value}[r][j] : 0.0f; }}")
+            body.emit(f"_Pragma(\"unroll\") for (int o = 32 / W; o < 32; o <<= 1) {{ _Pragma(\"unroll\") for (int j = 0; j < W; ++j) {name}[j] += __shfl_xor_sync(0xffffffffu, {name}[j], o); }}")
+            body.emit(f"if ((threadIdx.x & 31) < 32 / W && x0 < {m}) tk::st_row<W>({scratch} + ((int64_t)(x0 >> 5) * {n}LL + x1), nvalid, {name});")
+        else:
+            name = body.temp("ts")
+            chunks_n = -(-n // 32)
+            body.emit(f"float {name} = 0.0f;")
+            body.emit(f"_Pragma(\"unroll\") for (int r = 0; r < R; ++r) {{ _Pragma(\"unroll\") for (int j = 0; j < W; ++j) {name} += (j < nv[r]) ? {value}[r][j] : 0.0f; }}")
+            body.emit(f"_Pragma(\"unroll\") for (int o = 16; o; o >>= 1) {name} += __shfl_xor_sync(0xffffffffu, {name}, o);")
+            body.emit(f"if ((threadIdx.x & 31) == 0 && x0 < {m}) {scratch}[(int64_t)(x0 >> 5) * {chunks_n}LL + (x1 >> 5)] = {name};")
 
     def _tensor_map(self, operand, rows: int, depth: int, box_rows: int) -> tuple[int, bool]:
         """Register a tensor map for a [rows, depth] operand; returns (index, is_mn_major)."""
@@ -493,7 +523,7 @@ class _Emitter:
 
     def _finish_value(self, unit: Unit, body: _Body, acc: str, env: dict) -> None:
         op = unit.root
-        size = prod(unit.reduced)
+        size = unit.mean_count or prod(unit.reduced)
         value = acc if op.op == "sum" else (f"({acc} / {size}.0f)" if size else "NAN")
         root = body.temp("v")
         body.emit(f"float {root}[1] = {{{ROUND[op.output.dtype]}::rnd({value})}};")
@@ -514,7 +544,7 @@ class _Emitter:
             body.emit(f"if (o < {outputs}LL) {{")
             body.depth += 1
             body.emit("float acc = 0.0f;")
-            body.emit(f"for (int p = 0; p < {parts}; ++p) acc += {scratch}[(int64_t)p * {outputs}LL + o];")
+            body.emit(f"_Pragma(\"unroll 8\") for (int p = 0; p < {parts}; ++p) acc += {scratch}[(int64_t)p * {outputs}LL + o];")
             env: dict = {}
             self._finish_value(unit, body, "acc", env)
             coords = self._unravel("o", unit.kept, "x", body)
@@ -567,7 +597,7 @@ class _Emitter:
                 if unit.phase == "partial":
                     body.emit(f"tk::st_row<8>({scratch} + ((int64_t)part * {outputs}LL + o), 8, acc);")
                 else:
-                    op, rsize = unit.root, prod(unit.reduced)
+                    op, rsize = unit.root, unit.mean_count or prod(unit.reduced)
                     scale = "acc[j]" if op.op == "sum" else f"(acc[j] / {rsize}.0f)"
                     body.emit("float fin[8];")
                     body.emit(f"_Pragma(\"unroll\") for (int j = 0; j < 8; ++j) fin[j] = {ROUND[op.output.dtype]}::rnd({scale});")

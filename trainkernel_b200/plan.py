@@ -85,6 +85,21 @@ class Store:
 
 
 @dataclass
+class FusedReduce:
+    """A reduction whose partial sums are formed in a tensor-core GEMM's epilogue, from accumulator registers.
+
+    `mode` "cols": per 32-row chunk and column, the sum over the chunk's rows of member `buffer`, stored at
+    scratch[(row / 32), column].  `mode` "all": per 32 x 32 chunk the sum of all its elements, stored at
+    scratch[(row / 32) * ceil(N / 32) + column / 32].  The reduce unit that owned the reduction keeps only
+    its fixed-order finish over the partials.
+    """
+    mode: str
+    buffer: str
+    scratch: str
+    parts: int
+
+
+@dataclass
 class GemmOperand:
     buffer: str            # stored buffer the operand is read from
     dtype: str             # storage dtype
@@ -124,6 +139,9 @@ class Unit:
     vector: bool = False                   # thread strategy: 8 adjacent outputs per thread
     wait_barrier: int | None = None        # peers must have passed this grid barrier before the unit starts
     items: int = 1
+    fused: list = field(default_factory=list)   # gemm: FusedReduce entries evaluated in the epilogue
+    mean_count: int = 0                    # reduce over partials: the element count a mean divides by
+    no_split: bool = False                 # reduce over partials: one pass, never split again
 
     @property
     def writes(self) -> set[str]:
@@ -465,6 +483,39 @@ class Planner:
         strides += tuple(source.strides[d] for d in axes) if axes else (0,)
         unit.source = self._expr(space, Access(source.buffer, source.dtype, source.offset, strides), unit.index)
 
+    def _fuse_reduction(self, unit: Unit, dtypes: dict, shapes: dict, absorbed: dict) -> None:
+        """Move the summation of `unit` into the epilogue of the tensor-core GEMM that produces its operand."""
+        source = unit.source
+        if not isinstance(source, Load) or unit.root.op not in ("sum", "mean"):
+            return
+        access = source.access
+        host = self.claimed.get(access.buffer)
+        if host is None or host.kind != "gemm" or host.path != "tc" or access.offset != 0:
+            return
+        if host.pmaps.get(access.buffer) != (0, 1) or shapes[access.buffer] != host.dims:
+            return
+        m, n = host.dims
+        if m < 2 or n < 2:
+            return
+        if unit.kept == (n,) and unit.reduced == (m,) and access.strides == (1, n):
+            mode, parts, outputs = "cols", -(-m // 32), n
+        elif prod(unit.kept) == 1 and unit.reduced == (m, n) and access.strides[-2:] == (n, 1) and not any(access.strides[:-2]):
+            mode, parts, outputs = "all", -(-m // 32) * -(-n // 32), 1
+        else:
+            return
+        scratch = f"{unit.name}__partials"
+        dtypes[scratch], shapes[scratch] = "float32", (parts, outputs)
+        host.fused.append(FusedReduce(mode, access.buffer, scratch, parts))
+        absorbed.setdefault(access.buffer, set()).add(id(unit.root))
+        if mode == "cols":
+            unit.phase, unit.scratch, unit.parts = "finish", scratch, parts
+        else:
+            # the finish is itself a (small) reduction: one block sums the chunk partials in a fixed order
+            unit.mean_count = m * n
+            unit.no_split = True
+            unit.reduced = (parts,)
+            unit.source = Load(Access(scratch, "float32", 0, (0, 1)))
+
     # -- main pass -------------------------------------------------------------------
     def _plan_once(self) -> Plan:
         self.claimed: dict[str, Unit] = {}
@@ -531,17 +582,26 @@ class Planner:
         dtypes.update({op.output.buffer: op.output.dtype for op in self.ops})
         shapes = {spec.buffer: spec.shape for spec in program.inputs}
         shapes.update({op.output.buffer: op.output.shape for op in self.ops})
+        # Reductions over a value that a tensor-core GEMM's epilogue holds in registers (the loss terms, dY for
+        # the bias gradients) are summed there, chunk by chunk, instead of re-reading the value from memory.
+        absorbed: dict[str, set[int]] = {}
+        if self.fuse_epilogues:
+            for unit in units:
+                if unit.kind == "reduce":
+                    self._fuse_reduction(unit, dtypes, shapes, absorbed)
         for unit in units:
             own = {m.output.buffer for m in unit.members}
             if unit.root is not None:
                 own.add(unit.root.output.buffer)
             ordered = ([unit.root.output.buffer] if unit.root is not None else []) + [m.output.buffer for m in unit.members]
             for buffer in ordered:
-                outside = any(user.output.buffer not in own for user in users.get(buffer, []))
+                outside = any(user.output.buffer not in own and id(user) not in absorbed.get(buffer, ())
+                              for user in users.get(buffer, []))
                 if outside or buffer in self.output_buffers:
                     unit.stores.append(Store(buffer, dtypes[buffer]))
             # drop members that feed no store
-            needed = {s.buffer for s in unit.stores}
+            needed = {s.buffer for s in unit.stores} | {f.buffer for f in unit.fused}
+            unit.stores += [Store(f.scratch, "float32") for f in unit.fused]
             for member in reversed(unit.members):
                 if member.output.buffer in needed:
                     needed |= self._refs(unit.exprs[member.output.buffer])
@@ -859,10 +919,14 @@ class Planner:
     def _split_reductions(self, units: list[Unit], dtypes: dict, shapes: dict) -> list[Unit]:
         result: list[Unit] = []
         for unit in units:
-            if unit.kind != "reduce":
+            if unit.kind != "reduce" or unit.phase == "finish":
                 result.append(unit)
                 continue
             outputs, size = prod(unit.kept), prod(unit.reduced)
+            if unit.no_split:
+                unit.strategy, unit.parts = ("thread" if size <= 32 else "block"), 1
+                result.append(unit)
+                continue
             loads: list[Access] = []
             self._loads(unit.source, loads)
             wide = [a for a in loads if any(a.strides)]
