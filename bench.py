@@ -542,7 +542,7 @@ def main() -> None:
         torch.cuda.synchronize()
         a.record()
         for _ in range(5):
-            step.gradient.module.launch(flat, (step.loss, *step.views), step.gradient_workspace, stream)
+            step.gradient.module.launch(step.gradient.launch_inputs(flat), (step.loss, *step.views), step.gradient_workspace, stream)
         b.record()
         b.synchronize()
         kernel_ms = a.elapsed_time(b) / 5

@@ -81,6 +81,9 @@ int tk_module_invalidate_carried(tk_module* module, void* stream);
  * whoever loaded it (0 when never recorded).  Used by launch paths that must check what they are handed.
  * No counterpart in the reference (its launch derives both from the workspace tensor, trainkernel/codegen.py:866). */
 int tk_module_device(tk_module* module, int* out);
+/* Launches issued through this module so far, by any caller in the process: lets a caller that tracks
+ * carried values notice that somebody else launched the kernel in between.  No counterpart in the reference. */
+int tk_module_launches(tk_module* module, uint64_t* out);
 int tk_module_set_workspace_bytes(tk_module* module, size_t bytes);
 int tk_module_workspace_bytes(tk_module* module, size_t* out);
 

@@ -168,11 +168,11 @@ def test_peer_flag_wait_gives_up_and_reports():
     workspace = torch.empty(generated.workspace_elements, dtype=torch.float32, device=device)
     extra = [mine, mine, silent]
     stream = torch.cuda.current_stream(device).cuda_stream
-    module.launch((*state, x, t, *extra), outputs, workspace, stream)
+    module.launch(checker.launch_inputs((*state, x, t, *extra)), outputs, workspace, stream)
     with pytest.raises(RuntimeError, match=r"timed out \(code 6,"):
         checker.status()
     with pytest.raises(RuntimeError, match="tk_module_reset"):
-        module.launch((*state, x, t, *extra), outputs, workspace, stream)
+        module.launch(checker.launch_inputs((*state, x, t, *extra)), outputs, workspace, stream)
     assert lib.tk_module_reset(module.handle) == 0
     # the context is intact: an ordinary step of the same shapes matches the oracle
     work = workloads.build("c2", device="cuda")
@@ -182,3 +182,75 @@ def test_peer_flag_wait_gives_up_and_reports():
     step.runner.status()
     expected = oracle_outputs(step.program, (cpu.state, *cpu.batches[0]))
     assert_outputs_close(out, expected, REL_TOL[torch.bfloat16], "step after the timed-out launch")
+
+
+# ---------------------------------------------------------------------------------------------
+# BF16 weight copies carried from one launch to the next
+# ---------------------------------------------------------------------------------------------
+def _oracle_step(program, state, batch):
+    from oracle import interpreter
+    n = len(state)
+    out = interpreter.run(program, (*state, *batch))
+    return out, tuple(e.clone() for e in out[1 + n:])
+
+
+def test_carried_weight_copies_follow_every_edit_of_the_state():
+    """The step kernel keeps the BF16 copies of its master weights between launches and skips re-casting them
+    when the state tensors are untouched.  Every way of touching them must still give the oracle's result:
+    an in-place PyTorch operation (seen through the version counter), a write PyTorch cannot see followed by
+    `invalidate_carried()`, and a CUDA-graph replay that starts from restored state."""
+    tol = REL_TOL[torch.bfloat16]
+    work = workloads.build("c4", device="cuda")
+    cpu_program, _ = tk.capture(work.fn(), (work.state, *work.batches[0]))
+    compiled = tk.compile_training(work.fn(), (work.state, *work.batches[0]), stage_stamps=True)
+    runner = compiled.runner
+    assert runner.generated.carry_bytes == 2 * work.weight_elements and runner.carried is not None
+    state = work.state
+    reference = tuple(p.clone() for p in state)
+    first_stage = []
+
+    def step_and_check(label, batch):
+        nonlocal reference
+        expected, reference = _oracle_step(cpu_program, reference, batch)
+        out = compiled(state, *batch)
+        runner.status()
+        stamps = runner.stage_stamps()
+        first_stage.append(stamps[1] - stamps[0])
+        for index, (got, want) in enumerate(zip([out[0], *out[1], *out[2]], expected)):
+            err = float((got.float() - want.float()).abs().max()) / max(float(want.float().abs().max()), 1e-30)
+            assert err <= tol, f"{label}: output {index} is {err:.3e} from the oracle"
+
+    step_and_check("first launch (casts)", work.batches[0])
+    step_and_check("second launch (carried)", work.batches[1])
+    step_and_check("third launch (carried)", work.batches[2])
+    assert min(first_stage[1:]) < 0.6 * first_stage[0], f"the casting stage was not skipped: {first_stage}"
+    # an in-place edit PyTorch can see
+    with torch.no_grad():
+        state[0].mul_(0.5)
+        state[2].add_(0.01)
+    reference = tuple(p.clone() for p in state)
+    step_and_check("after an in-place edit", work.batches[3])
+    # a write the version counters do not see, declared by the caller
+    state[4].data.mul_(2.0)
+    runner.invalidate_carried()
+    reference = tuple(p.clone() for p in state)
+    step_and_check("after invalidate_carried", work.batches[0])
+    # graph replays start from whatever state they find
+    saved = [p.clone() for p in state]
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(3):
+            compiled(state, *work.batches[i])
+    results = []
+    for scale in (1.0, 0.25):
+        for p, s in zip(state, saved):
+            p.copy_(s * scale)
+        reference = tuple(p.clone() for p in state)
+        graph.replay()
+        torch.cuda.synchronize()
+        runner.status()
+        for i in range(3):
+            _, reference = _oracle_step(cpu_program, reference, work.batches[i])
+        for index, (got, want) in enumerate(zip(state, reference)):
+            err = float((got - want).abs().max()) / max(float(want.abs().max()), 1e-30)
+            assert err <= tol, f"replay from state x {scale}: parameter {index} is {err:.3e} from the oracle"

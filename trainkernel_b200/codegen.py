@@ -84,6 +84,7 @@ class GeneratedKernel:
     world: int = 1                        # ranks the kernel exchanges with (1: no exchange stages)
     multicast: bool = False               # exchanges through the multicast mapping (one more extra input)
     symmetric_bytes: int = 0              # size of the peer-mapped buffer the kernel expects after the program inputs
+    carry_bytes: int = 0                  # size of the carry buffer the kernel expects as its LAST input (0: none)
 
 
 class _Body:
@@ -121,6 +122,11 @@ class _Emitter:
         self.trace_stage = None
         self.rows = False
         self.background = plan.background
+        exchanging = plan.symmetric_bytes > 0
+        # kernel inputs beyond the program's own: [symmetric buffer, every rank's mapping of it, (multicast mapping)], [carry buffer]
+        self.exchange_inputs = 1 + plan.world + int(plan.multicast) if exchanging else 0
+        self.carry_input = len(plan.program.inputs) + self.exchange_inputs
+        self.extra_inputs = self.exchange_inputs + (1 if plan.carry_bytes else 0)
 
     # -- addressing ------------------------------------------------------------------
     def pointer(self, buffer: str, dtype: str, const: bool) -> str:
@@ -133,6 +139,9 @@ class _Emitter:
             return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>(P.out[{where[1]}])"
         if where[0] == "scatter":
             raise ValueError(f"trainkernel: {buffer} is staged for a cross-rank exchange and cannot be read in place")
+        if where[0] == "carry":
+            local = f"reinterpret_cast<uint8_t*>(const_cast<void*>(P.in[{self.carry_input}]))"
+            return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>({local} + {where[1]}ULL)"
         if where[0] == "sym":
             local = f"reinterpret_cast<uint8_t*>(const_cast<void*>(P.in[{len(self.plan.program.inputs)}]))"
             return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>({local} + {where[1]}ULL)"
@@ -390,10 +399,13 @@ class _Emitter:
         s_row, s_k = operand.strides
         k_major = (s_k == 1 or depth == 1) and s_row % 8 == 0 and (s_row >= depth or rows == 1)
         base = self.plan.storage[operand.buffer]
+        extra = 0
+        if base[0] == "carry":                      # lives in the carry buffer, which the kernel receives as one more input
+            base, extra = ("in", self.carry_input), base[1]
         if k_major:
-            spec = TensorMapSpec(base, operand.offset * 2, depth, rows, max(s_row, 8) * 2, 64, box_rows)
+            spec = TensorMapSpec(base, extra + operand.offset * 2, depth, rows, max(s_row, 8) * 2, 64, box_rows)
         else:
-            spec = TensorMapSpec(base, operand.offset * 2, rows, depth, max(s_k, 8) * 2, 64, 64)
+            spec = TensorMapSpec(base, extra + operand.offset * 2, rows, depth, max(s_k, 8) * 2, 64, 64)
         self.maps.append(spec)
         return len(self.maps) - 1, not k_major
 
@@ -736,6 +748,13 @@ class _Emitter:
             for unit in ordered:
                 if unit in background:
                     continue
+                if unit.carried:
+                    body.emit(f"if (!carried) {{   // {unit.name}: skipped when the previous launch left this value behind")
+                    body.depth += 1
+                    self.point(unit, body, bases[id(unit)])
+                    body.depth -= 1
+                    body.emit("}")
+                    continue
                 if background and unit.kind != "gemm" or (background and unit.kind == "gemm" and unit.path not in ("tc", "tc2")):
                     if not getattr(self, "_drained", None) == stage:
                         self._drained = stage
@@ -760,7 +779,7 @@ class _Emitter:
                 self._drained = stage
                 body.emit(f"tk::bg_drain<{bg}>(c, P);   // whatever background work is left, by all warps")
         exchanging = plan.symmetric_bytes > 0
-        n_in = max(1, len(plan.program.inputs) + (1 + plan.world + int(plan.multicast) if exchanging else 0))
+        n_in = max(1, len(plan.program.inputs) + self.extra_inputs)
         n_out = max(1, len(plan.program.outputs))
         n_maps = max(1, len(self.maps))
         n_maps_used = len(self.maps)
@@ -804,9 +823,14 @@ class _Emitter:
             entry.append(f"    if (threadIdx.x < {n_maps_used}) tk::tma_prefetch_desc(&P.maps[threadIdx.x]);")
         if exchanging:
             entry.append(f"    tk::dp_init(c.dp, const_cast<void*>(P.in[{len(plan.program.inputs)}]));")
+        if plan.carry_bytes:
+            # read before the first stage boundary: the word is rewritten by whichever block finishes this launch first
+            entry.append("    const bool carried = (P.flags & tk::kTrustCarried) != 0u && P.status[tk::kCarriedWord] == 1u && P.status[0] == 0u;")
         if stage_stamps:
             entry.append("    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[0] = tk::global_timer_ns();")
         tail = []
+        if plan.carry_bytes:
+            tail.append("    if (blockIdx.x == 0 && threadIdx.x == 0) P.status[tk::kCarriedWord] = (c.aborted() || c.grid_aborted()) ? 0u : 1u;")
         if stage_stamps:
             tail.append(f"    __syncthreads();\n    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[{plan.stages}] = tk::global_timer_ns();")
         if exchanging:
@@ -840,7 +864,8 @@ def _check_broadcasts(program: Program) -> None:
 def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = None, fuse_pointwise: bool = True,
                  fuse_epilogues: bool = True, max_blocks: int | None = None, tensor_cores: bool = True,
                  block_n: int | None = None, two_cta: bool | None = None, world: int = 1,
-                 background: bool = False, multicast: bool = False, cluster_barrier: bool | None = None) -> Plan:
+                 background: bool = False, multicast: bool = False, cluster_barrier: bool | None = None,
+                 carry_shadows: bool = True) -> Plan:
     """Validate, canonicalise and plan `program` (no code is emitted)."""
     validate(program)
     from .passes import canonicalize_transposed_mm
@@ -869,7 +894,7 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
             raise ValueError("trainkernel: inplace outputs must be computed values, not input views")
     return Planner(program, inplace_outputs=mapping, fuse_pointwise=fuse_pointwise, fuse_epilogues=fuse_epilogues,
                    max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n, two_cta=two_cta, world=world,
-                   background=background, multicast=multicast, cluster_barrier=cluster_barrier).plan()
+                   background=background, multicast=multicast, cluster_barrier=cluster_barrier, carry=carry_shadows).plan()
 
 
 _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shared_skew", "split_k_gemv",
@@ -881,7 +906,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
              two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
              multicast: bool = False, cluster_barrier: bool | None = None, trace_stage: int | None = None,
-             **reference_knobs) -> GeneratedKernel:
+             carry_shadows: bool = True, **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -904,6 +929,13 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     `stage_stamps=True`) also records six role-level timestamps of the first single-CTA tensor-core
     tile of stage `s` (`CompiledProgram.role_trace`).
 
+    `carry_shadows` (default on): a value that is a bare cast of in-place state and feeds tensor-core
+    GEMMs (the BF16 copy of an FP32 master weight) is kept in a carry buffer between launches; the unit
+    that commits the updated state also stores its cast there, and the casting unit of the next launch
+    is skipped when the launch carries `TK_LAUNCH_TRUST_CARRIED` (`GeneratedKernel.carry_bytes` > 0
+    means the kernel takes that buffer as its last input).  A module with carried values must not be
+    launched on two streams at once.
+
     With `world > 1` the kernel takes `1 + world` extra inputs after the program's own: this rank's
     symmetric buffer, then every rank's mapping of it in rank order.  `multicast=True` adds one more,
     this rank's pointer to the NVSwitch multicast mapping of the buffer, and exchanges through
@@ -920,7 +952,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     plan = plan_program(program, inplace_outputs=inplace_outputs, fuse_pointwise=fuse_pointwise,
                         fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n,
                         two_cta=two_cta, world=world, background=background, multicast=multicast,
-                        cluster_barrier=cluster_barrier)
+                        cluster_barrier=cluster_barrier, carry_shadows=carry_shadows)
     # Fixed-size tables the kernel indexes by stage or barrier number: the stamp area, and (with peers) the
     # 64 flag words per rank in the symmetric buffer's header, laid out from word 16.
     if stage_stamps and plan.stages > MAX_STAMPED_STAGES:
@@ -939,14 +971,16 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
             raise ValueError("trainkernel: raster_group must be between 1 and 64")
         emitter.raster_group = raster_group
     source = emitter.kernel(stage_stamps)
-    extra_inputs = 1 + plan.world + int(plan.multicast) if plan.symmetric_bytes else 0
+    extra_inputs = emitter.extra_inputs
     n_in, n_out = max(1, len(plan.program.inputs) + extra_inputs), max(1, len(plan.program.outputs))
     n_maps = max(1, len(emitter.maps))
     param_bytes = 128 * n_maps + 8 * (n_in + n_out) + 8 * 6
     per_stage: dict[int, int] = {}
     for unit in plan.units:
         per_stage[unit.stage] = per_stage.get(unit.stage, 0) + unit.items
-    materialized = sum((1 if u.root is not None and u.phase != "partial" else 0) + len(u.members) for u in plan.units)
+    # IR operations that run as (part of) a unit; the re-created casts of carried values are not program operations
+    materialized = sum((1 if u.root is not None and u.phase != "partial" else 0)
+                       + sum(1 for member in u.members if not member.name.endswith("__next")) for u in plan.units)
     from .plan import SM_COUNT  # noqa: F401
     dyn = 0
     if emitter.needs_simt:
@@ -979,4 +1013,5 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         world=plan.world,
         multicast=plan.multicast,
         symmetric_bytes=plan.symmetric_bytes,
+        carry_bytes=plan.carry_bytes,
     )

@@ -128,6 +128,7 @@ struct tk_module {
     size_t param_bytes = 0;
     int ordinal = 0;                  // device ordinal the module was loaded on
     std::atomic<size_t> workspace_bytes{0};  // what the kernel's plan needs (0: not recorded)
+    std::atomic<uint64_t> launches{0};       // launches issued through this module
     std::atomic<int> faulted{0};      // tk_module_status saw an error; launches are refused until tk_module_reset
     std::atomic<unsigned long long> capture_id{0};   // last stream capture a launch was recorded into
 
@@ -314,6 +315,7 @@ int tk_module_launch_flags(tk_module* m, const void* const* inputs, void* const*
     void* params[1] = {block};
     if (int rc = check(g_driver.cuLaunchKernelEx_(&config, m->function, params, nullptr), "cuLaunchKernelEx")) return rc;
     g_launches.fetch_add(1);
+    m->launches.fetch_add(1);
     return 0;
 }
 
@@ -396,6 +398,12 @@ int tk_module_reset(tk_module* m) {
 int tk_module_device(tk_module* m, int* out) {
     if (!m || !out) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_device");
     *out = m->ordinal;
+    return 0;
+}
+
+int tk_module_launches(tk_module* m, uint64_t* out) {
+    if (!m || !out) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_launches");
+    *out = m->launches.load();
     return 0;
 }
 

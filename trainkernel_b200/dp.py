@@ -171,7 +171,7 @@ class ShardedTrainingStep:
         self.gradient._validate_inputs(flat)
         state = flat[:self.count]
         stream = torch.cuda.current_stream(self.device).cuda_stream
-        self.gradient.module.launch(flat, (self.loss, *self.views), self.gradient_workspace, stream)
+        self.gradient.module.launch(self.gradient.launch_inputs(flat), (self.loss, *self.views), self.gradient_workspace, stream)
         if dist.is_initialized() and dist.get_world_size(self.group) > 1:
             dist.all_reduce(self.flat, op=dist.ReduceOp.AVG, group=self.group)
             dist.all_reduce(self.loss, op=dist.ReduceOp.AVG, group=self.group)
@@ -181,7 +181,7 @@ class ShardedTrainingStep:
         else:
             outputs = state
             grads = tuple(self.views)
-        self.update.module.launch(state + tuple(self.views), outputs, self.update_workspace, stream)
+        self.update.module.launch(self.update.launch_inputs(state + tuple(self.views)), outputs, self.update_workspace, stream)
         torch.autograd.graph.increment_version(list(state))
         return tree_unflatten([self.loss, *grads, *state], self.output_tree)
 
@@ -302,6 +302,7 @@ class FusedShardedTrainingStep:
             torch.cuda.current_stream(device)
             self.module = runtime._Module(self.generated, cubin, device)
         self._checker = runtime.CompiledProgram(program, self.generated, self.module, device, {1 + n + i: i for i in range(n)})
+        self.carried = self._checker.carried
         self.loss = torch.zeros((), dtype=torch.float32, device=device)
         self.gradients = tuple(torch.empty(spec.shape, dtype=getattr(torch, spec.dtype), device=device)
                                for spec in program.outputs[1:1 + n])
@@ -324,8 +325,14 @@ class FusedShardedTrainingStep:
         self.steps_launched += 1
         state = flat[:self.count]
         stream = torch.cuda.current_stream(self.device).cuda_stream
-        self.module.launch((*flat, *self._extra), (self.loss, *self.gradients, *state), self.workspace, stream)
+        if self.carried is not None:
+            self.module.launch((*flat, *self._extra, self.carried.buffer), (self.loss, *self.gradients, *state), self.workspace, stream,
+                               self.carried.flags(state))
+        else:
+            self.module.launch((*flat, *self._extra), (self.loss, *self.gradients, *state), self.workspace, stream)
         torch.autograd.graph.increment_version(list(state))
+        if self.carried is not None:
+            self.carried.launched(state)
         return tree_unflatten([self.loss, *self.gradients, *state], self.output_tree)
 
     def status(self) -> None:
@@ -356,6 +363,8 @@ class FusedShardedTrainingStep:
         if self.world > 1:
             dist.barrier(self.group)
         self.module.lib.tk_module_reset(self.module.handle)
+        if self.carried is not None:
+            self.carried.invalidate()
         header = self.symmetric[:1024]
         header.zero_()
         self.symmetric[1] = self.rank
@@ -371,6 +380,7 @@ class FusedShardedTrainingStep:
         torch.cuda.synchronize(self.device)
         self.module = None
         self._checker = None
+        self.carried = None
         self._extra = []
         self._handle = None
         self.symmetric = None

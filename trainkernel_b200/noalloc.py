@@ -63,7 +63,9 @@ def launch_static_workspace(runner: runtime.CompiledProgram, inputs, outputs) ->
     # the same argument checks as every other launch path; none of them allocates
     runner._validate_inputs(inputs)
     runner._check_outputs(inputs, outputs)
-    ins = (ctypes.c_void_p * module.n_in)(*[t.data_ptr() for t in inputs])
+    # buffers the compiled program owns (made when it was compiled, not now) complete the kernel's input list;
+    # this entry point passes no launch flags, so values carried over from an earlier launch are recomputed
+    ins = (ctypes.c_void_p * module.n_in)(*[t.data_ptr() for t in runner.launch_inputs(inputs)])
     outs = (ctypes.c_void_p * module.n_out)(*[t.data_ptr() for t in outputs])
     message = ctypes.create_string_buffer(512)
     stream = torch.cuda.current_stream(runner.device).cuda_stream
@@ -72,3 +74,5 @@ def launch_static_workspace(runner: runtime.CompiledProgram, inputs, outputs) ->
                                                        module.grid, stream, message, len(message))
     if code:
         raise RuntimeError(message.value.decode() or f"trainkernel: static-workspace launch failed with code {code}")
+    if runner.inplace_outputs:
+        torch.autograd.graph.increment_version([inputs[i] for i in set(runner.inplace_outputs.values())])

@@ -140,6 +140,7 @@ class Unit:
     wait_barrier: int | None = None        # peers must have passed this grid barrier before the unit starts
     items: int = 1
     fused: list = field(default_factory=list)   # gemm: FusedReduce entries evaluated in the epilogue
+    carried: bool = False                  # point: a cast of in-place state whose result the updating unit re-creates for the next launch
     mean_count: int = 0                    # reduce over partials: the element count a mean divides by
     no_split: bool = False                 # reduce over partials: one pass, never split again
 
@@ -198,14 +199,16 @@ class Plan:
     background: bool = False               # run memory-bound units inside the epilogue warps of tensor-core stages
     multicast: bool = False                # exchange through the NVSwitch multicast mapping (multimem) instead of scattering
     cluster_blocks: int = 0                # > 0: the whole grid is ONE thread-block cluster of this many blocks, stages end in the hardware cluster barrier
+    carry_bytes: int = 0                   # size of the buffer that keeps derived values (BF16 weight copies) from one launch to the next
 
 
 class Planner:
     def __init__(self, program: Program, *, inplace_outputs: dict[int, int] | None = None,
                  fuse_pointwise: bool = True, fuse_epilogues: bool = True, max_blocks: int | None = None,
                  tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None, world: int = 1, background: bool = False,
-                 multicast: bool = False, cluster_barrier: bool | None = None):
+                 multicast: bool = False, cluster_barrier: bool | None = None, carry: bool = True):
         self.program = program
+        self.carry = carry
         self.cluster_barrier = cluster_barrier
         self.inplace = dict(inplace_outputs or {})
         self.fuse_pointwise = fuse_pointwise
@@ -699,6 +702,50 @@ class Planner:
             if slot in self.inplace and slot not in staged:
                 staged[slot] = self.inplace[slot]
 
+        # Values derived from in-place state by a bare cast (the BF16 copies of FP32 master weights that the
+        # tensor-core GEMMs read) are carried from one launch to the next: the unit that commits the updated
+        # state also stores its cast into the SAME location, so the next launch can skip the casting unit when
+        # it is told that nobody touched the state in between.  Legal when every reader of the copy can be
+        # ordered strictly before that unit (the same constraint-graph test as a direct commit).
+        carry_bytes = 0
+        if self.carry and direct:
+            slot_of_target = {target: slot for slot, target in direct.items()}
+            for unit in list(units):
+                if unit.kind != "point" or len(unit.members) != 1 or unit.members[0].op != "cast" or len(unit.stores) != 1:
+                    continue
+                cast = unit.members[0]
+                source = cast.inputs[0]
+                copy = cast.output.buffer
+                if not isinstance(source, TensorSpec) or source.buffer not in self.input_index or copy in storage:
+                    continue
+                target = self.input_index[source.buffer]
+                slot = slot_of_target.get(target)
+                if slot is None or not _dense(source) or source.shape != program.inputs[target].shape or cast.output.shape != source.shape:
+                    continue
+                updated = program.outputs[slot].buffer
+                owner = writer[updated]
+                if owner.phase == "partial" or updated not in owner.pmaps or _squeeze(shapes[updated]) != _squeeze(cast.output.shape):
+                    continue
+                readers = [u for u in units if u is not unit and copy in u.reads]
+                if owner in readers:
+                    continue
+                trial = ordering + [(reader, owner) for reader in readers]
+                if not self._assign_stages(units, writer, trial):
+                    self._assign_stages(units, writer, ordering)
+                    continue
+                ordering = trial
+                name = copy + "__next"
+                value = TensorSpec(updated, shapes[updated], dtypes[updated], row_major(shapes[updated]), updated)
+                again = Operation(name, "cast", (value,), TensorSpec(name, shapes[updated], cast.output.dtype, row_major(shapes[updated]), name))
+                owner.members.append(again)
+                owner.pmaps[name] = owner.pmaps[updated]
+                owner.exprs[name] = Apply(again, (Ref(updated),))
+                owner.stores.append(Store(name, cast.output.dtype))
+                dtypes[name], shapes[name] = cast.output.dtype, shapes[updated]
+                storage[copy] = storage[name] = ("carry", carry_bytes)
+                carry_bytes += -(-max(1, prod(cast.output.shape)) * ELEMENT_BYTES[cast.output.dtype] // ALIGN) * ALIGN
+                unit.carried = True
+
         # copy units for outputs that are views, duplicates, or staged commits
         position = len(self.ops)
         for slot, spec in copies:
@@ -831,7 +878,8 @@ class Planner:
             grid = cluster_blocks
         return Plan(program, sorted(units, key=lambda u: (u.stage, u.index)), stage_count, storage, dtypes, shapes,
                     max(total, ALIGN), inlined, direct, staged, native, grid, tc_units, tc_units > 0, two_cta,
-                    self.world, symmetric if symmetric > SYM_HEADER else 0, tuple(sorted(signal)), self.background, self.multicast, cluster_blocks)
+                    self.world, symmetric if symmetric > SYM_HEADER else 0, tuple(sorted(signal)), self.background, self.multicast, cluster_blocks,
+                    carry_bytes)
 
     # -- helpers ---------------------------------------------------------------------
     def _refs(self, expr) -> set[str]:

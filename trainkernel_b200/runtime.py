@@ -93,6 +93,7 @@ def library() -> ctypes.CDLL:
         lib.tk_module_launch_flags.argtypes = [p, ctypes.POINTER(p), ctypes.POINTER(p), p, i32, p, u32]
         lib.tk_module_invalidate_carried.argtypes = [p, p]
         lib.tk_module_device.argtypes = [p, ctypes.POINTER(i32)]
+        lib.tk_module_launches.argtypes = [p, ctypes.POINTER(u64)]
         lib.tk_module_set_workspace_bytes.argtypes = [p, ctypes.c_size_t]
         lib.tk_module_workspace_bytes.argtypes = [p, ctypes.POINTER(ctypes.c_size_t)]
         lib.tk_module_resource_usage.argtypes = [p, ctypes.POINTER(ctypes.c_int64)]
@@ -202,12 +203,17 @@ class _Module:
         self.n_in = max(1, generated.input_count)
         self.n_out = max(1, generated.output_count)
 
-    def launch(self, inputs, outputs, workspace: torch.Tensor, stream: int) -> None:
+    def launch(self, inputs, outputs, workspace: torch.Tensor, stream: int, flags: int = 0) -> None:
         ins = (ctypes.c_void_p * self.n_in)(*[t.data_ptr() for t in inputs])
         outs = (ctypes.c_void_p * self.n_out)(*[t.data_ptr() for t in outputs])
-        code = self.lib.tk_module_launch(self.handle, ins, outs, workspace.data_ptr(), self.grid, stream)
+        code = self.lib.tk_module_launch_flags(self.handle, ins, outs, workspace.data_ptr(), self.grid, stream, flags)
         if code:
             _raise(code)
+
+    def launches(self) -> int:
+        count = ctypes.c_uint64()
+        self.lib.tk_module_launches(self.handle, ctypes.byref(count))
+        return int(count.value)
 
     def __del__(self):
         handle, self.handle = getattr(self, "handle", None), None
@@ -216,6 +222,44 @@ class _Module:
                 self.lib.tk_module_unload(handle)
             except Exception:
                 pass
+
+
+TRUST_CARRIED = 1          # TK_LAUNCH_TRUST_CARRIED
+
+
+class CarriedState:
+    """Host-side bookkeeping for values a kernel carries from one launch to the next.
+
+    A kernel with `GeneratedKernel.carry_bytes > 0` keeps the BF16 copies of its FP32 master weights
+    in a buffer owned by this object and re-creates them while it commits the updated masters, so
+    the next launch may skip casting them again — but only if nobody changed the state tensors in
+    between.  PyTorch counts in-place modifications per tensor (`Tensor._version`): a launch is
+    told to trust the carried values exactly when it gets the same state tensors (same addresses)
+    whose version counters still have the values this object recorded after the previous launch.
+    A write the counters cannot see (a raw pointer handed to another library) needs `invalidate()`.
+    Under stream capture the runtime shim additionally ignores the flag for the first launch of
+    every capture, so a replayed graph always starts from the state it finds.
+    """
+
+    def __init__(self, nbytes: int, device: torch.device, module: Any = None) -> None:
+        self.buffer = torch.empty(max(1, nbytes), dtype=torch.uint8, device=device)
+        self.module = module
+        self.seen: tuple | None = None
+
+    def _snapshot(self, targets) -> tuple:
+        # the module's own launch count is part of it: a launch issued by anyone else rewrote the buffer
+        count = self.module.launches() if self.module is not None and hasattr(self.module, "launches") else 0
+        return (count, *((t.data_ptr(), t._version) for t in targets))
+
+    def flags(self, targets) -> int:
+        return TRUST_CARRIED if self.seen is not None and self.seen == self._snapshot(targets) else 0
+
+    def launched(self, targets) -> None:
+        """Call after the launch has bumped the targets' version counters."""
+        self.seen = self._snapshot(targets)
+
+    def invalidate(self) -> None:
+        self.seen = None
 
 
 class CompiledProgram:
@@ -237,6 +281,30 @@ class CompiledProgram:
         # what every call compares its arguments with, looked up once
         self._input_meta = [(spec.shape, spec.strides, getattr(torch, spec.dtype)) for spec in program.inputs]
         self._output_meta = [(spec.shape, getattr(torch, spec.dtype)) for spec in program.outputs]
+        self._targets = sorted(set(self.inplace_outputs.values()))
+        self.carried = CarriedState(generated.carry_bytes, device, module) if getattr(generated, "carry_bytes", 0) else None
+
+    def invalidate_carried(self) -> None:
+        """Make the next launch recompute what the previous one left behind (the BF16 weight copies): for
+        callers that overwrite the state through something PyTorch's version counters do not see."""
+        if self.carried is not None:
+            self.carried.invalidate()
+
+    def _launch(self, inputs: tuple[torch.Tensor, ...], outputs, workspace: torch.Tensor) -> None:
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        targets = [inputs[i] for i in self._targets]
+        if self.carried is not None:
+            self.module.launch((*inputs, self.carried.buffer), outputs, workspace, stream, self.carried.flags(targets))
+        else:
+            self.module.launch(inputs, outputs, workspace, stream)
+        if targets:
+            torch.autograd.graph.increment_version(targets)
+        if self.carried is not None:
+            self.carried.launched(targets)
+
+    def launch_inputs(self, inputs: tuple[torch.Tensor, ...]) -> tuple:
+        """The kernel's full input list for `inputs`: the program's inputs plus the buffers this object owns."""
+        return (*inputs, self.carried.buffer) if self.carried is not None else tuple(inputs)
 
     # -- introspection -------------------------------------------------------------
     def resource_usage(self) -> dict[str, int]:
@@ -364,10 +432,7 @@ class CompiledProgram:
     def run_into(self, *inputs: torch.Tensor, buffers: ExecutionBuffers) -> tuple[torch.Tensor, ...]:
         self._validate_inputs(inputs)
         self._check_buffers(inputs, buffers)
-        stream = torch.cuda.current_stream(self.device).cuda_stream
-        self.module.launch(inputs, buffers.outputs, buffers.workspace, stream)
-        if self.inplace_outputs:
-            torch.autograd.graph.increment_version([inputs[i] for i in self.inplace_outputs.values()])
+        self._launch(inputs, buffers.outputs, buffers.workspace)
         return buffers.outputs
 
     def __call__(self, *inputs: torch.Tensor) -> tuple[torch.Tensor, ...]:
@@ -382,10 +447,7 @@ class CompiledProgram:
                     if other != index and value.numel() and value.untyped_storage().data_ptr() == storage:
                         raise ValueError("trainkernel: inplace target must not alias another input")
         buffers = self._fresh_buffers(inputs)
-        stream = torch.cuda.current_stream(self.device).cuda_stream
-        self.module.launch(inputs, buffers.outputs, buffers.workspace, stream)
-        if self.inplace_outputs:
-            torch.autograd.graph.increment_version([inputs[i] for i in self.inplace_outputs.values()])
+        self._launch(inputs, buffers.outputs, buffers.workspace)
         return buffers.outputs
 
 
