@@ -202,9 +202,9 @@ def test_carried_weight_copies_follow_every_edit_of_the_state():
     tol = REL_TOL[torch.bfloat16]
     work = workloads.build("c4", device="cuda")
     cpu_program, _ = tk.capture(work.fn(), (work.state, *work.batches[0]))
-    compiled = tk.compile_training(work.fn(), (work.state, *work.batches[0]), stage_stamps=True)
+    compiled = tk.compile_training(work.fn(), (work.state, *work.batches[0]), stage_stamps=True, carry_shadows=True)
     runner = compiled.runner
-    assert runner.generated.carry_bytes == 2 * work.weight_elements and runner.carried is not None
+    assert runner.generated.carry_bytes == 2 * 2 * work.weight_elements and runner.carried is not None
     state = work.state
     reference = tuple(p.clone() for p in state)
     first_stage = []

@@ -28,15 +28,19 @@ def test_tiny_mlp_schedule_shares_stages_and_commits_directly():
     by_stage = {}
     for stage, kind, name, path, items in g.units:
         by_stage.setdefault(stage, []).append(name)
-    # The BF16 copy of W2 is carried to the next launch: dW2 (mm_2), whose epilogue rewrites it, runs one stage
-    # after dX (mm_3), the copy's last reader, and shares that stage with dW1 (mm_4).
-    assert g.carry_bytes == 2 * (128 * 256 + 256 * 128) and g.input_count == len(program.inputs) + 1
-    assert "mm_3" in by_stage[3] and {"mm_2", "mm_4"} <= set(by_stage[4])
-    assert g.source.count("if (!carried)") == 2
-    plain = generate(program, inplace_outputs=inplace, carry_shadows=False)
-    assert plain.carry_bytes == 0 and plain.stages == 5 and "carried" not in plain.source
-    stages = {name: stage for stage, kind, name, path, items in plain.units}
-    assert stages["mm_2"] == stages["mm_3"] == 3            # without carrying, dW and dX of a layer share a stage
+    assert {"mm_2", "mm_3"} <= set(by_stage[3])          # dW and dX of a layer share a stage
+    # a program this small casts its weights in every launch
+    assert g.carry_bytes == 0 and "carried" not in g.source
+    # when asked to, the BF16 copies of W1 and W2 are carried to the next launch in two copies each (read one, write the other)
+    carrying = generate(program, inplace_outputs=inplace, carry_shadows=True)
+    assert carrying.carry_bytes == 2 * 2 * (128 * 256 + 256 * 128) and carrying.input_count == len(program.inputs) + 1
+    assert carrying.source.count("if (!carried)") == 2 and "tk_carry_phase ?" in carrying.source and carrying.stages == 5
+    # one copy, rewritten in place: dW2 (mm_2), whose epilogue rewrites W2's copy, runs one stage after dX
+    # (mm_3), the copy's last reader, and shares that stage with dW1 (mm_4)
+    single = generate(program, inplace_outputs=inplace, carry_shadows="reorder")
+    stages = {name: stage for stage, kind, name, path, items in single.units}
+    assert single.carry_bytes == 2 * (128 * 256 + 256 * 128) and "tk_carry_phase" not in single.source
+    assert stages["mm_3"] == 3 and stages["mm_2"] == stages["mm_4"] == 4 and single.stages == 5
     assert "tcgen05" not in g.source and "tk::gemm_tc<" in g.source   # device library is included, not pasted
 
 
@@ -155,7 +159,8 @@ def test_medium_mlp_plan_fits_and_uses_wide_tiles():
     assert g.cluster == 2 and "tk::gemm_tc2<" in g.source and "tk::gemm_tc<" not in g.source   # pair tiles everywhere
     single = generate(program, inplace_outputs={9 + i: i for i in range(8)}, two_cta=False)
     assert single.cluster == 1 and "tk::gemm_tc<256" in single.source
-    assert len(g.tensor_maps) == 22 and g.param_bytes <= 4096
+    # 22 operand maps, 7 of them twice (the weights' BF16 copies exist in two copies); the shim's parameter block holds 8 KiB
+    assert len(g.tensor_maps) == 29 and g.param_bytes <= 8192 and g.carry_bytes == 2 * 2 * 201326592
 
 
 def test_exchange_units_overlap_backward_gemms_and_precede_updates():
@@ -176,8 +181,10 @@ def test_exchange_units_overlap_backward_gemms_and_precede_updates():
     assert plan.storage["mm_2"][0] == "scatter" and plan.storage["mm_2_avg"][0] == "sym" and plan.symmetric_bytes > 4096
     assert len(plan.direct_commits) == 4                                           # updates still commit in place
     g = generate(exchanged, inplace_outputs=inplace, world=2)
-    # program inputs, this rank's symmetric buffer, both ranks' mappings of it, and the carry buffer last
-    assert g.input_count == len(program.inputs) + 1 + 2 + 1 and g.world == 2 and g.carry_bytes > 0
+    # program inputs, this rank's symmetric buffer, both ranks' mappings of it
+    assert g.input_count == len(program.inputs) + 1 + 2 and g.world == 2 and g.carry_bytes == 0
+    with_carry = generate(exchanged, inplace_outputs=inplace, world=2, carry_shadows=True)      # the carry buffer comes last
+    assert with_carry.input_count == len(program.inputs) + 1 + 2 + 1 and with_carry.carry_bytes > 0
     assert "tk::exchange_mean<tk::BF16, 2>" in g.source and "tk::dp_signal" in g.source and "tk::dp_wait" in g.source
     assert "tk::st_row_scatter<W, 2, __nv_bfloat16>" in g.source          # dW epilogue pushes straight to the owner
     assert runtime.build_cubin(g.source)[:4] == b"\x7fELF"
@@ -185,7 +192,7 @@ def test_exchange_units_overlap_backward_gemms_and_precede_updates():
         generate(exchanged, inplace_outputs=inplace, world=9)
     # through the NVSwitch multicast mapping: contributions stay local, one more pointer, no scatter
     switch = generate(exchanged, inplace_outputs=inplace, world=2, multicast=True)
-    assert switch.multicast and switch.input_count == len(program.inputs) + 1 + 2 + 1 + 1
+    assert switch.multicast and switch.input_count == len(program.inputs) + 1 + 2 + 1
     assert f"tk::exchange_mean_mc<tk::BF16, 2>(c, &P.in[{len(program.inputs) + 1}], P.in[{len(program.inputs) + 3}]" in switch.source
     assert "st_row_scatter" not in switch.source and "tk::dp_wait" in switch.source
     assert switch.symmetric_bytes <= g.symmetric_bytes and switch.stages == g.stages

@@ -141,7 +141,8 @@ class _Emitter:
             raise ValueError(f"trainkernel: {buffer} is staged for a cross-rank exchange and cannot be read in place")
         if where[0] == "carry":
             local = f"reinterpret_cast<uint8_t*>(const_cast<void*>(P.in[{self.carry_input}]))"
-            return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>({local} + {where[1]}ULL)"
+            offset = f"{where[1]}ULL" if where[1] == where[2] else f"(tk_carry_phase ? {where[2]}ULL : {where[1]}ULL)"
+            return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>({local} + {offset})"
         if where[0] == "sym":
             local = f"reinterpret_cast<uint8_t*>(const_cast<void*>(P.in[{len(self.plan.program.inputs)}]))"
             return f"reinterpret_cast<{'const ' if const else ''}{ctype}*>({local} + {where[1]}ULL)"
@@ -394,20 +395,29 @@ class _Emitter:
             body.emit(f"_Pragma(\"unroll\") for (int o = 16; o; o >>= 1) {name} += __shfl_xor_sync(0xffffffffu, {name}, o);")
             body.emit(f"if ((threadIdx.x & 31) == 0 && x0 < {m}) {scratch}[(int64_t)(x0 >> 5) * {chunks_n}LL + (x1 >> 5)] = {name};")
 
-    def _tensor_map(self, operand, rows: int, depth: int, box_rows: int) -> tuple[int, bool]:
-        """Register a tensor map for a [rows, depth] operand; returns (index, is_mn_major)."""
+    def _tensor_map(self, operand, rows: int, depth: int, box_rows: int) -> tuple[str, bool]:
+        """Register the tensor map(s) for a [rows, depth] operand; returns (index expression, is_mn_major).
+
+        An operand in the carry buffer with two copies gets one map per copy, and the index expression
+        picks the copy this launch reads.
+        """
         s_row, s_k = operand.strides
         k_major = (s_k == 1 or depth == 1) and s_row % 8 == 0 and (s_row >= depth or rows == 1)
         base = self.plan.storage[operand.buffer]
-        extra = 0
+        extras = [0]
         if base[0] == "carry":                      # lives in the carry buffer, which the kernel receives as one more input
-            base, extra = ("in", self.carry_input), base[1]
-        if k_major:
-            spec = TensorMapSpec(base, extra + operand.offset * 2, depth, rows, max(s_row, 8) * 2, 64, box_rows)
-        else:
-            spec = TensorMapSpec(base, extra + operand.offset * 2, rows, depth, max(s_k, 8) * 2, 64, 64)
-        self.maps.append(spec)
-        return len(self.maps) - 1, not k_major
+            extras = [base[1]] if base[1] == base[2] else [base[1], base[2]]
+            base = ("in", self.carry_input)
+        indices = []
+        for extra in extras:
+            if k_major:
+                spec = TensorMapSpec(base, extra + operand.offset * 2, depth, rows, max(s_row, 8) * 2, 64, box_rows)
+            else:
+                spec = TensorMapSpec(base, extra + operand.offset * 2, rows, depth, max(s_k, 8) * 2, 64, 64)
+            self.maps.append(spec)
+            indices.append(len(self.maps) - 1)
+        index = str(indices[0]) if len(indices) == 1 else f"(tk_carry_phase ? {indices[1]} : {indices[0]})"
+        return index, not k_major
 
     def gemm(self, unit: Unit, body: _Body, base: int, bg: str = "tk::NoBg") -> None:
         epi = self.functor(unit)
@@ -705,6 +715,8 @@ class _Emitter:
                     body.emit(f"if (blockIdx.x == 0 && threadIdx.x < {plan.world}) tk::dp_signal(c.dp, &P.in[{len(plan.program.inputs) + 1}], threadIdx.x, {stage - 1});")
                 if stage_stamps:
                     body.emit(f"if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[{stage}] = tk::global_timer_ns();")
+            if stage == 1 and plan.carry_pingpong:
+                body.emit("if (blockIdx.x == 0 && threadIdx.x == 0) P.status[tk::kCarryPhaseWord] = tk_carry_phase ^ 1u;   // every block has read the word by now")
             body.emit(f"// ---- stage {stage} ----")
             base = 0
             members = [u for u in plan.units if u.stage == stage]
@@ -801,7 +813,8 @@ class _Emitter:
             "    uint32_t flags;",
             "};",
             "",
-        ]
+        ] + (["__shared__ uint32_t tk_carry_phase;   // copy of the carried values this launch reads (the other one is written)", ""]
+             if plan.carry_pingpong else [])
         entry = [
             f"extern \"C\" __global__ void __launch_bounds__({THREADS}, 1) tk_step(const __grid_constant__ Params P) {{",
             "    extern __shared__ uint8_t dyn_smem[];",
@@ -826,6 +839,10 @@ class _Emitter:
         if plan.carry_bytes:
             # read before the first stage boundary: the word is rewritten by whichever block finishes this launch first
             entry.append("    const bool carried = (P.flags & tk::kTrustCarried) != 0u && P.status[tk::kCarriedWord] == 1u && P.status[0] == 0u;")
+        if plan.carry_pingpong:
+            # which copy of the carried values this launch READS; block 0 flips the word after the first stage boundary
+            entry.append("    if (threadIdx.x == 0) tk_carry_phase = P.status[tk::kCarryPhaseWord] & 1u;")
+            entry.append("    __syncthreads();")
         if stage_stamps:
             entry.append("    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[0] = tk::global_timer_ns();")
         tail = []
@@ -865,7 +882,7 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
                  fuse_epilogues: bool = True, max_blocks: int | None = None, tensor_cores: bool = True,
                  block_n: int | None = None, two_cta: bool | None = None, world: int = 1,
                  background: bool = False, multicast: bool = False, cluster_barrier: bool | None = None,
-                 carry_shadows: bool = True) -> Plan:
+                 carry_shadows: bool | str | None = None) -> Plan:
     """Validate, canonicalise and plan `program` (no code is emitted)."""
     validate(program)
     from .passes import canonicalize_transposed_mm
@@ -906,7 +923,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
              two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
              multicast: bool = False, cluster_barrier: bool | None = None, trace_stage: int | None = None,
-             carry_shadows: bool = True, **reference_knobs) -> GeneratedKernel:
+             carry_shadows: bool | str | None = None, **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -929,12 +946,17 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     `stage_stamps=True`) also records six role-level timestamps of the first single-CTA tensor-core
     tile of stage `s` (`CompiledProgram.role_trace`).
 
-    `carry_shadows` (default on): a value that is a bare cast of in-place state and feeds tensor-core
+    `carry_shadows` (default: decided by the planner, on for kernels of large GEMMs, where the casting
+    stage costs a quarter of a millisecond of HBM traffic, off for small ones, whose weight-gradient
+    stages are bound by their epilogue stores and lose more to the extra store than the skipped stage
+    saves): a value that is a bare cast of in-place state and feeds tensor-core
     GEMMs (the BF16 copy of an FP32 master weight) is kept in a carry buffer between launches; the unit
     that commits the updated state also stores its cast there, and the casting unit of the next launch
     is skipped when the launch carries `TK_LAUNCH_TRUST_CARRIED` (`GeneratedKernel.carry_bytes` > 0
-    means the kernel takes that buffer as its last input).  A module with carried values must not be
-    launched on two streams at once.
+    means the kernel takes that buffer as its last input).  `True` / `"pingpong"` keeps two copies of
+    every carried value (a launch reads one and writes the other; the schedule is unchanged),
+    `"reorder"` keeps one and orders its rewrite behind its last reader, `False` casts in every
+    launch.  A module with carried values must not be launched on two streams at once.
 
     With `world > 1` the kernel takes `1 + world` extra inputs after the program's own: this rank's
     symmetric buffer, then every rank's mapping of it in rank order.  `multicast=True` adds one more,

@@ -50,6 +50,7 @@ constexpr int kStampPeerWait = 192;    // + s: nanoseconds block 0 waited for pe
 constexpr int kStampTrace = 248;       // + point: role-level trace of one tile
 constexpr uint32_t kTrustCarried = 1u; // launch flag: state untouched since the previous launch of this module
 constexpr int kCarriedWord = 8;        // status word: values carried over from the previous launch are valid
+constexpr int kCarryPhaseWord = 9;     // status word: which of the two copies of the carried values the next launch reads
 
 enum : uint32_t {
     kOk = 0,

@@ -200,15 +200,18 @@ class Plan:
     multicast: bool = False                # exchange through the NVSwitch multicast mapping (multimem) instead of scattering
     cluster_blocks: int = 0                # > 0: the whole grid is ONE thread-block cluster of this many blocks, stages end in the hardware cluster barrier
     carry_bytes: int = 0                   # size of the buffer that keeps derived values (BF16 weight copies) from one launch to the next
+    carry_pingpong: bool = False           # carried values have two copies; a launch reads one and writes the other
 
 
 class Planner:
     def __init__(self, program: Program, *, inplace_outputs: dict[int, int] | None = None,
                  fuse_pointwise: bool = True, fuse_epilogues: bool = True, max_blocks: int | None = None,
                  tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None, world: int = 1, background: bool = False,
-                 multicast: bool = False, cluster_barrier: bool | None = None, carry: bool = True):
+                 multicast: bool = False, cluster_barrier: bool | None = None, carry: bool | str | None = None):
         self.program = program
-        self.carry = carry
+        if carry not in (None, True, False, "pingpong", "reorder"):
+            raise ValueError("trainkernel: carry_shadows must be None, True, False, 'pingpong' or 'reorder'")
+        self.carry = "pingpong" if carry is True else carry
         self.cluster_barrier = cluster_barrier
         self.inplace = dict(inplace_outputs or {})
         self.fuse_pointwise = fuse_pointwise
@@ -486,6 +489,14 @@ class Planner:
         strides += tuple(source.strides[d] for d in axes) if axes else (0,)
         unit.source = self._expr(space, Access(source.buffer, source.dtype, source.offset, strides), unit.index)
 
+    def _wants_pair_tiles(self, units: list[Unit]) -> bool:
+        """Two-CTA (256 x 256) pair tiles: when every tensor-core GEMM is large enough to keep the clusters busy."""
+        tc = [u for u in units if u.kind == "gemm" and u.path in ("tc", "tc2")]
+        eligible = bool(tc) and all(u.mnk[0] >= 256 and u.mnk[1] >= 256 for u in tc)
+        if self.two_cta is not None:
+            return bool(self.two_cta and eligible)
+        return eligible and min(-(-u.mnk[0] // 256) * -(-u.mnk[1] // 256) for u in tc) >= 64
+
     def _fuse_reduction(self, unit: Unit, dtypes: dict, shapes: dict, absorbed: dict) -> None:
         """Move the summation of `unit` into the epilogue of the tensor-core GEMM that produces its operand."""
         source = unit.source
@@ -704,10 +715,19 @@ class Planner:
 
         # Values derived from in-place state by a bare cast (the BF16 copies of FP32 master weights that the
         # tensor-core GEMMs read) are carried from one launch to the next: the unit that commits the updated
-        # state also stores its cast into the SAME location, so the next launch can skip the casting unit when
-        # it is told that nobody touched the state in between.  Legal when every reader of the copy can be
-        # ordered strictly before that unit (the same constraint-graph test as a direct commit).
+        # state also stores its cast, so the next launch can skip the casting unit when it is told that nobody
+        # touched the state in between.  Two forms.  "pingpong": every carried value has two copies; a launch
+        # reads copy r (a device-side word that flips every launch) and writes copy 1 - r, so the schedule does
+        # not change.  "reorder": one copy, rewritten in place, legal when every reader of the copy can be
+        # ordered strictly before the rewriting unit (the same constraint-graph test as a direct commit),
+        # which moves dW of a layer one stage behind dX of the layer below.
         carry_bytes = 0
+        # Left to itself (None) the planner carries only in kernels of large GEMMs (the ones that get two-CTA pair
+        # tiles): there the casting stage is a quarter of a millisecond of HBM traffic and the extra BF16 store
+        # hides behind a long main loop.  Measured on B200, the small MLP (batch 512) LOSES 5 to 11 us per step
+        # with carrying, because its dW stages are bound by their epilogue stores.
+        if self.carry is None:
+            self.carry = "pingpong" if self._wants_pair_tiles(units) else False
         if self.carry and direct:
             slot_of_target = {target: slot for slot, target in direct.items()}
             for unit in list(units):
@@ -727,13 +747,14 @@ class Planner:
                 if owner.phase == "partial" or updated not in owner.pmaps or _squeeze(shapes[updated]) != _squeeze(cast.output.shape):
                     continue
                 readers = [u for u in units if u is not unit and copy in u.reads]
-                if owner in readers:
-                    continue
-                trial = ordering + [(reader, owner) for reader in readers]
-                if not self._assign_stages(units, writer, trial):
-                    self._assign_stages(units, writer, ordering)
-                    continue
-                ordering = trial
+                if self.carry == "reorder":
+                    if owner in readers:
+                        continue
+                    trial = ordering + [(reader, owner) for reader in readers]
+                    if not self._assign_stages(units, writer, trial):
+                        self._assign_stages(units, writer, ordering)
+                        continue
+                    ordering = trial
                 name = copy + "__next"
                 value = TensorSpec(updated, shapes[updated], dtypes[updated], row_major(shapes[updated]), updated)
                 again = Operation(name, "cast", (value,), TensorSpec(name, shapes[updated], cast.output.dtype, row_major(shapes[updated]), name))
@@ -742,8 +763,14 @@ class Planner:
                 owner.exprs[name] = Apply(again, (Ref(updated),))
                 owner.stores.append(Store(name, cast.output.dtype))
                 dtypes[name], shapes[name] = cast.output.dtype, shapes[updated]
-                storage[copy] = storage[name] = ("carry", carry_bytes)
-                carry_bytes += -(-max(1, prod(cast.output.shape)) * ELEMENT_BYTES[cast.output.dtype] // ALIGN) * ALIGN
+                size = -(-max(1, prod(cast.output.shape)) * ELEMENT_BYTES[cast.output.dtype] // ALIGN) * ALIGN
+                if self.carry == "pingpong":
+                    # ("carry", offset when the phase word is 0, offset when it is 1)
+                    storage[copy], storage[name] = ("carry", carry_bytes, carry_bytes + size), ("carry", carry_bytes + size, carry_bytes)
+                    carry_bytes += 2 * size
+                else:
+                    storage[copy] = storage[name] = ("carry", carry_bytes, carry_bytes)
+                    carry_bytes += size
                 unit.carried = True
 
         # copy units for outputs that are views, duplicates, or staged commits
@@ -847,8 +874,7 @@ class Planner:
         # clusters busy; a kernel uses one cta_group for all of its tcgen05 instructions.
         tc = [u for u in units if u.kind == "gemm" and u.path == "tc"]
         pair_tiles = [-(-u.mnk[0] // 256) * -(-u.mnk[1] // 256) for u in tc]
-        eligible = bool(tc) and all(u.mnk[0] >= 256 and u.mnk[1] >= 256 for u in tc)
-        two_cta = eligible and min(pair_tiles) >= 64 if self.two_cta is None else bool(self.two_cta and eligible)
+        two_cta = self._wants_pair_tiles(units)
         if two_cta:
             for unit, tiles in zip(tc, pair_tiles):
                 unit.path, unit.block_n, unit.items = "tc2", 256, 2 * tiles
@@ -879,7 +905,7 @@ class Planner:
         return Plan(program, sorted(units, key=lambda u: (u.stage, u.index)), stage_count, storage, dtypes, shapes,
                     max(total, ALIGN), inlined, direct, staged, native, grid, tc_units, tc_units > 0, two_cta,
                     self.world, symmetric if symmetric > SYM_HEADER else 0, tuple(sorted(signal)), self.background, self.multicast, cluster_blocks,
-                    carry_bytes)
+                    carry_bytes, bool(carry_bytes) and self.carry == "pingpong")
 
     # -- helpers ---------------------------------------------------------------------
     def _refs(self, expr) -> set[str]:
