@@ -89,7 +89,7 @@ def kernel_sources() -> dict[str, str]:
         for multicast in (False, True):
             name = f"medium_fused_n{world}" + ("_multicast" if multicast else "")
             sources[name] = codegen.generate(fused, inplace_outputs={1 + count + i: i for i in range(count)}, world=world,
-                                             multicast=multicast).source
+                                             multicast=multicast, background=True).source
     return sources
 
 
@@ -396,6 +396,9 @@ def main() -> None:
                         help="N = 1: launch the step kernel without the cooperative-launch attribute (its grid already "
                              "fits the idle device and its waits are bounded); for hardware profilers that cannot "
                              "replay cooperative cluster launches")
+    parser.add_argument("--no-stream-warps", action="store_true",
+                        help="N > 1, fused: generate the step kernel without the four stream warps per block that run the "
+                             "gradient exchange and the FP32 updates beside the GEMM tiles (for A/B measurements)")
     parser.add_argument("--no-multicast", action="store_true",
                         help="N > 1, fused: never exchange through the NVSwitch multicast mapping (multimem); "
                              "contributions are then scattered to their owners with plain peer stores")
@@ -439,7 +442,8 @@ def main() -> None:
             # should the blocks not all be resident after all, give up on a barrier after 0.2 s instead of 2 s
             runtime.library().tk_module_set_timeout(step.runner.module.handle, 200_000_000)
     elif args.dp == "fused":
-        step = dp.FusedShardedTrainingStep(work.fn(), (state, x0, t0), multicast=False if args.no_multicast else None)
+        step = dp.FusedShardedTrainingStep(work.fn(), (state, x0, t0), multicast=False if args.no_multicast else None,
+                                           background=not args.no_stream_warps)
         kernels_per_step = step.kernels_per_step
         status = step.status
         generated = step.generated
@@ -474,7 +478,7 @@ def main() -> None:
                 barrier()
                 work = workloads.mlp_workload(work.name, MEDIUM_SIZES, MEDIUM_BATCH, seed=0, device=device, rows=rows)
                 state = work.state
-                step = dp.FusedShardedTrainingStep(work.fn(), (state, *work.batches[0]), multicast=False)
+                step = dp.FusedShardedTrainingStep(work.fn(), (state, *work.batches[0]), multicast=False, background=not args.no_stream_warps)
                 status, generated = step.status, step.generated
                 step(state, *work.batches[0])
     barrier()

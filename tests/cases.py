@@ -142,6 +142,9 @@ CASES = {
     "mlp_2cta": mlp_case((512, 1024, 768, 512), 512, two_cta=True),
     "mlp_1cta": mlp_case((512, 1024, 768, 512), 512, two_cta=False),
     "mlp_2cta_background": mlp_case((512, 1024, 768, 512), 512, two_cta=True, background=True),
+    # stream warps with real work: the weight casts are not carried, so they run beside the forward GEMMs
+    "mlp_2cta_stream_warps": mlp_case((512, 1024, 768, 512), 512, two_cta=True, background=True, carry_shadows=False),
+    "mlp_1cta_stream_warps": mlp_case((512, 1024, 768, 512), 512, two_cta=False, background=True, carry_shadows=False),
     # fusion boundaries (reference: tests/test_epilogues_gpu.py, tests/test_side_epilogues.py)
     "observable_product": function_case(lambda a, b: (a @ b, torch.relu(a @ b) + 1.0), [(40, 24), (24, 56)]),
     "transposed_operand_broadcast_chain": function_case(lambda a, b, row, col: torch.relu(a.t() @ b + row) * col, [(24, 40), (24, 56), (56,), (40, 1)]),

@@ -10,7 +10,8 @@ pytestmark = pytest.mark.gpu
 
 GEMM_CASES = [name for name in cases.CASES if name.startswith(("gemm_", "gemm2_", "gemv_"))]
 STEP_CASES = ["c1", "c1_grid_barrier", "c2", "c2_grid_barrier", "c3_one_cluster", "c2_nofuse", "c2_notc", "c3", "c3_labels", "c4", "gemv", "mlp_f32", "mlp_bf16", "mlp_f16",
-              "mlp_f32_one_block", "linear_module", "mlp_2cta", "mlp_1cta", "mlp_2cta_background"]
+              "mlp_f32_one_block", "linear_module", "mlp_2cta", "mlp_1cta", "mlp_2cta_background", "mlp_2cta_stream_warps",
+              "mlp_1cta_stream_warps"]
 GENERAL_CASES = ["partial_reduce", "big_reduce", "long_reduce", "views_out", "addmm_scaled", "addmm_scaled_bf16",
                  "addmm_beta0_nan_bias", "observable_product", "transposed_operand_broadcast_chain", "rounding_boundary_bf16",
                  "branched_outputs_one_product", "huge_reduction", "huge_reduction_bf16", "original_and_update"]
@@ -173,15 +174,18 @@ def test_split_step_without_a_process_group_matches_oracle(exchange):
     assert [p.data_ptr() for p in state] == pointers
 
 
-def test_fused_exchange_step_with_one_rank_matches_oracle_and_replays():
+@pytest.mark.parametrize("stream_warps", [False, True])
+def test_fused_exchange_step_with_one_rank_matches_oracle_and_replays(stream_warps):
     """The one-kernel data-parallel form (exchange stages inside the kernel) on a single rank:
-    flags, epochs and the pull/reduce/push path all run, with this GPU as its own only peer."""
+    flags, epochs and the pull/reduce/push path all run, with this GPU as its own only peer; with
+    stream warps the exchange and the FP32 updates run in warps 6..9 beside the GEMM tiles."""
     from trainkernel_b200 import dp, workloads
     import trainkernel_b200 as tk
     from oracle import interpreter
     work = workloads.build("c2", seed=2, device="cuda")
     cpu = workloads.build("c2", seed=2, device="cpu")
-    step = dp.FusedShardedTrainingStep(work.fn(), (work.state, *work.batches[0]))
+    step = dp.FusedShardedTrainingStep(work.fn(), (work.state, *work.batches[0]), background=stream_warps)
+    assert step.generated.threads == (320 if stream_warps else 192)
     assert step.generated.symmetric_bytes > 4096 and "tk::exchange_mean<" in step.generated.source
     program, _ = tk.capture(cpu.fn(), (cpu.state, *cpu.batches[0]))
     ref_state = tuple(cpu.state)

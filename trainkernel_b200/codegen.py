@@ -20,6 +20,7 @@ from math import prod
 from .ir import Operation, Program, TensorSpec, row_major, validate
 from .plan import (ELEMENT_BYTES, SYM_HEADER, THREADS, Access, Apply, Const, Iota, Load, Plan, Planner, Ref, Unit, point_unroll)
 
+STREAM_WARPS = 4                 # tk::kStreamWarps: extra warps of a kernel generated with background=True
 MAX_STAMPED_STAGES = 55          # stamp area: 64 words per table, the peer-wait table shares its block with the role trace
 FLAG_WORDS_PER_RANK = 64         # cross-rank "passed barrier k" words per rank in the symmetric header
 
@@ -122,6 +123,7 @@ class _Emitter:
         self.trace_stage = None
         self.rows = False
         self.background = plan.background
+        self.threads = THREADS + (32 * STREAM_WARPS if plan.background else 0)
         exchanging = plan.symmetric_bytes > 0
         # kernel inputs beyond the program's own: [symmetric buffer, every rank's mapping of it, (multicast mapping)], [carry buffer]
         self.exchange_inputs = 1 + plan.world + int(plan.multicast) if exchanging else 0
@@ -729,9 +731,10 @@ class _Emitter:
             # cross-rank ordering first: background work may start as soon as the stage does
             for barrier in sorted({u.wait_barrier for u in members if u.wait_barrier is not None}):
                 body.emit(f"tk::dp_wait(c, c.dp, {plan.world}, {barrier});   // every rank has passed grid barrier {barrier}")
-            # memory-bound units that the epilogue warps run while they wait for the tensor pipe
-            tensor_units = [u for u in ordered if u.kind == "gemm" and u.path in ("tc", "tc2")]
-            background = [u for u in ordered if tensor_units and self.background and
+            # Memory-bound units (gradient exchange, flat pointwise streams such as the FP32 updates) of a kernel
+            # with stream warps: warps 6..9 of every block work through them while warps 0..5 run the stage's
+            # other units (the GEMM tiles above all); whoever finishes first helps with what is left.
+            background = [u for u in ordered if self.background and not u.carried and
                           (u.kind == "exchange" or (u.kind == "point" and prod(u.dims) and self._flat_ok(u)))]
             bg = "tk::NoBg"
             if background:
@@ -746,20 +749,22 @@ class _Emitter:
                         self.point_item(unit, fn, "tid")
                     self.functors.append(f"// {unit.name} ({unit.kind}) of stage {stage}, one 32-thread slice of item `it`\n"
                                          f"static __device__ __noinline__ void bg_{stage}_{k}(const Params& P, tk::Ctx& c, int64_t it, int tid) {{\n{fn.text()}\n}}\n")
-                    b, n = bases[id(unit)], unit.items
-                    totals.append(f"tk::owned_items({b}LL, {n}LL)")
-                    runs.append(f"        {{ const int64_t n = tk::owned_items({b}LL, {n}LL) * {THREADS // 32}; if (o < n) {{ bg_{stage}_{k}(P, c, tk::first_item({b}LL) + (o / {THREADS // 32}) * gridDim.x, "
+                    b0, n = bases[id(unit)], unit.items
+                    totals.append(f"tk::owned_items({b0}LL, {n}LL)")
+                    runs.append(f"        {{ const int64_t n = tk::owned_items({b0}LL, {n}LL) * {THREADS // 32}; if (o < n) {{ bg_{stage}_{k}(P, c, tk::first_item({b0}LL) + (o / {THREADS // 32}) * gridDim.x, "
                                 f"(int)(o % {THREADS // 32}) * 32 + lane); return; }} o -= n; }}")
                 self.functors.append(
                     f"struct Bg_{stage} {{\n    static constexpr bool kActive = true;\n"
                     f"    static __device__ __forceinline__ int total() {{ return (int)({THREADS // 32} * ({' + '.join(totals)})); }}\n"
                     f"    static __device__ __forceinline__ void run(const Params& P, tk::Ctx& c, int ordinal, int lane) {{\n        int64_t o = ordinal;\n"
                     + "\n".join(runs) + "\n    }\n};\n")
-                body.emit(f"if (threadIdx.x == 0) {{ shared_state.bg_next = 0; shared_state.bg_total = {bg}::total(); }}")
+                body.emit(f"if (threadIdx.x == 0) {{ shared_state.bg_next = shared_state.bg_back = shared_state.bg_taken = 0; shared_state.bg_total = {bg}::total(); }}")
                 body.emit("__syncthreads();")
-            for unit in ordered:
-                if unit in background:
-                    continue
+            foreground = [u for u in ordered if u not in background]
+            if self.background and foreground:
+                body.emit("if (c.warp < tk::kWorkerWarps) {   // stream warps go straight to the background pieces")
+                body.depth += 1
+            for unit in foreground:
                 if unit.carried:
                     body.emit(f"if (!carried) {{   // {unit.name}: skipped when the previous launch left this value behind")
                     body.depth += 1
@@ -767,10 +772,6 @@ class _Emitter:
                     body.depth -= 1
                     body.emit("}")
                     continue
-                if background and unit.kind != "gemm" or (background and unit.kind == "gemm" and unit.path not in ("tc", "tc2")):
-                    if not getattr(self, "_drained", None) == stage:
-                        self._drained = stage
-                        body.emit(f"tk::bg_drain<{bg}>(c, P);   // whatever background work is left, by all warps")
                 body.emit("{")
                 body.depth += 1
                 if unit.kind == "exchange":
@@ -780,16 +781,18 @@ class _Emitter:
                     body.emit(self._exchange_call(unit, peers, "", "c", f"{bases[id(unit)]}LL, {unit.items}LL"))
                 elif unit.kind == "gemm":
                     body.emit(f"// {unit.name}: {unit.root.op} {unit.mnk} via {unit.path}")
-                    self.gemm(unit, body, bases[id(unit)], bg if unit.path in ("tc", "tc2") else "tk::NoBg")
+                    self.gemm(unit, body, bases[id(unit)])
                 elif unit.kind == "reduce":
                     self.reduce(unit, body, bases[id(unit)])
                 else:
                     self.point(unit, body, bases[id(unit)])
                 body.depth -= 1
                 body.emit("}")
-            if background and getattr(self, "_drained", None) != stage:
-                self._drained = stage
-                body.emit(f"tk::bg_drain<{bg}>(c, P);   // whatever background work is left, by all warps")
+            if self.background and foreground:
+                body.depth -= 1
+                body.emit("}")
+            if background:
+                body.emit(f"tk::bg_drain<{bg}>(c, P);   // the stream warps' whole stage; the other warps help once their units are done")
         exchanging = plan.symmetric_bytes > 0
         n_in = max(1, len(plan.program.inputs) + self.extra_inputs)
         n_out = max(1, len(plan.program.outputs))
@@ -816,7 +819,7 @@ class _Emitter:
         ] + (["__shared__ uint32_t tk_carry_phase;   // copy of the carried values this launch reads (the other one is written)", ""]
              if plan.carry_pingpong else [])
         entry = [
-            f"extern \"C\" __global__ void __launch_bounds__({THREADS}, 1) tk_step(const __grid_constant__ Params P) {{",
+            f"extern \"C\" __global__ void __launch_bounds__({self.threads}, 1) tk_step(const __grid_constant__ Params P) {{",
             "    extern __shared__ uint8_t dyn_smem[];",
             "    __shared__ tk::SharedState shared_state;",
         ]
@@ -931,10 +934,12 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     `inline_input_casts`) have no meaning on this back end; they are accepted so
     existing call sites keep working, and ignored.  `hopper_wgmma=True` is rejected.
 
-    `background=True` lets the epilogue warps of tensor-core stages execute that stage's flat
-    pointwise and exchange units while they wait for the tensor pipe (and places weight-shadow
-    casts next to the GEMM before their first use).  Measured on B200 it did not pay off — one warp
-    per piece keeps too few loads in flight and delays the epilogues — so it is off by default.
+    `background=True` gives every block four more warps (320 threads instead of 192), the stream
+    warps, which execute the flat pointwise and exchange units of each stage while the other six
+    warps run the stage's GEMM tiles (and places weight-shadow casts next to the GEMM before their
+    first use).  It is what lets a batch-sharded step overlap its gradient exchange and its
+    HBM-bound FP32 updates with the backward GEMMs; single-GPU steps have nothing to overlap and
+    leave it off.
 
     `cluster_barrier` (default: decided from the amount of work) runs the whole kernel as ONE
     thread-block cluster of at most 8 blocks whose stages end in the hardware cluster barrier instead
@@ -1020,6 +1025,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         grid_barriers=plan.stages - 1,
         direct_outputs=len(plan.native_outputs) + len(plan.direct_commits),
         direct_state_commits=len(plan.direct_commits),
+        threads=emitter.threads,
         dynamic_smem=dyn,
         grid=plan.grid,
         tensor_maps=tuple(emitter.maps),

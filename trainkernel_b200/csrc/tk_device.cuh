@@ -21,6 +21,10 @@ namespace tk {
 
 constexpr int kThreads = 192;          // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
 constexpr int kEpiThreads = 128;
+constexpr int kWorkerWarps = kThreads / 32;   // warps that run a stage's units; work items are cut for kThreads threads
+// A kernel generated with stream warps is launched with kThreads + 32 * kStreamWarps threads: warps 6..9 do
+// nothing but the stage's memory-bound pieces (gradient exchange, FP32 updates) while warps 0..5 run its GEMMs.
+constexpr int kStreamWarps = 4;
 constexpr int BM = 128;                // UMMA M
 constexpr int BK = 64;                 // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
@@ -143,8 +147,10 @@ struct SharedState {
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort;
-    int bg_next;          // next background work ordinal of this block in the current stage
-    int bg_total;         // number of background ordinals this block owns in the current stage
+    int bg_next;          // background pieces of this block taken from the front of the current stage's list
+    int bg_back;          // ... and from its back
+    int bg_taken;         // pieces handed out so far (front and back together)
+    int bg_total;         // number of background pieces this block owns in the current stage
     float reduce[32];
 };
 
@@ -494,13 +500,17 @@ __device__ __forceinline__ void st_row_stream(float* p, int nvalid, const float*
 template <int W, typename T16>
 __device__ __forceinline__ void st_row_stream(T16* p, int nvalid, const float* v) { st_row<W>(p, nvalid, v); }
 
-// Block-wide FP32 sum; the total is valid in thread 0.  All threads of the block must call it.
+// Barrier among the kThreads worker threads (warps 0..5) only: stream warps, where a kernel has them, are
+// busy elsewhere and must not be waited for.  In a kernel of kThreads threads it is a block barrier.
+__device__ __forceinline__ void worker_sync() { asm volatile("bar.sync 1, %0;" :: "n"(kThreads) : "memory"); }
+
+// FP32 sum over the worker threads; the total is valid in thread 0.  All kThreads worker threads must call it.
 __device__ __forceinline__ float block_sum(Ctx& c, float v) {
 #pragma unroll
     for (int o = 16; o; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
-    __syncthreads();
+    worker_sync();
     if (c.lane == 0) c.sh->reduce[c.warp] = v;
-    __syncthreads();
+    worker_sync();
     float total = 0.0f;
     if (threadIdx.x == 0) {
 #pragma unroll
@@ -777,22 +787,29 @@ __device__ __forceinline__ void exchange_mean_mc(Ctx& c, const void* const* peer
 
 // ----------------------------------------------------------------------------
 // Background work.  Memory-bound units of a stage (flat pointwise streams, exchange units) are cut
-// into per-warp pieces that the epilogue warps execute while they would otherwise wait for the
-// tensor pipe, so HBM and NVLink traffic overlaps the MMAs of the same stage.  A stage's functor
-// Bg maps an ordinal of this block to (unit, item, 32-thread slice); ordinals are handed out with
-// a shared-memory counter, and whatever is left when the GEMM tiles are done is drained by all warps.
+// into per-warp pieces that the block's STREAM WARPS (warps 6..9 of a kernel generated with them)
+// execute while warps 0..5 run the stage's GEMM tiles, so HBM and NVLink traffic overlaps the MMAs
+// of the same stage on every SM.  A stage's functor Bg maps an ordinal of this block to (unit,
+// item, 32-thread slice); ordinals are handed out with a shared-memory counter, and whatever is
+// left when the GEMM tiles are done is drained by all warps.
 // ----------------------------------------------------------------------------
 struct NoBg {
     static constexpr bool kActive = false;
     template <typename Params> static __device__ __forceinline__ void run(const Params&, Ctx&, int, int) {}
 };
 
+// The list is worked from both ends: the pieces at the front are the HBM-bound streams, the ones at the back
+// the exchanges that are bound by NVLink, and warps coming from either side keep both busy at once.
 template <typename Bg, typename Params>
-__device__ __forceinline__ bool bg_step(Ctx& c, const Params& P) {
-    int ordinal = 0;
-    if (c.lane == 0) ordinal = atomicAdd(&c.sh->bg_next, 1);
+__device__ __forceinline__ bool bg_step(Ctx& c, const Params& P, bool from_back) {
+    int ordinal = -1;
+    if (c.lane == 0 && !c.aborted()) {              // one lane decides for the warp
+        const int total = *reinterpret_cast<volatile int*>(&c.sh->bg_total);
+        if (atomicAdd(&c.sh->bg_taken, 1) < total)
+            ordinal = from_back ? total - 1 - atomicAdd(&c.sh->bg_back, 1) : atomicAdd(&c.sh->bg_next, 1);
+    }
     ordinal = __shfl_sync(0xffffffffu, ordinal, 0);
-    if (ordinal >= *reinterpret_cast<volatile int*>(&c.sh->bg_total)) return false;
+    if (ordinal < 0) return false;
     Bg::run(P, c, ordinal, c.lane);
     return true;
 }
@@ -800,7 +817,8 @@ template <typename Bg, typename Params>
 __device__ __forceinline__ void bg_drain(Ctx& c, const Params& P) {
     if constexpr (Bg::kActive) {
         __syncwarp();
-        while (bg_step<Bg>(c, P)) {}
+        const bool from_back = c.warp >= kWorkerWarps + kStreamWarps / 2;
+        while (bg_step<Bg>(c, P, from_back)) {}
     }
 }
 // Number of items of a unit (n items starting at list position `base`) that this block owns.
@@ -938,7 +956,7 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
             }
         }
         __syncwarp();
-    } else {
+    } else if (c.warp < kWorkerWarps) {
         const int quarter = c.warp & 3;                // TMEM lanes this warp may read
         for (int64_t t = first_item(item_base); t < tiles && !c.aborted(); t += step) {
             int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
@@ -952,9 +970,6 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
                 int pm, pn; tile_coords(t + step, tiles_m, tiles_n, pm, pn);
                 const int prow = pm * BM + quarter * 32 + c.lane;
                 if (prow < M && pn * BN < N) Epi::prefetch(P, prow, pn * BN, min(BN, N - pn * BN));
-            }
-            if constexpr (Bg::kActive) {
-                while (!__all_sync(0xffffffffu, mbar_try(&sh->tmem_full[c.acc], c.acc_phase))) { if (!bg_step<Bg>(c, P)) break; }
             }
             if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
             tc_fence_after();
@@ -1002,7 +1017,7 @@ __device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm,
         float acc[2][4] = {};
         for (int k0 = 0; k0 < K; k0 += kSimtK) {
             const int depth = min(kSimtK, K - k0);
-            __syncthreads();
+            worker_sync();
             // Stage A[32, depth] and B[depth, 32].  Positions are decomposed against the fixed staging
             // depth (shifts and masks, no division by a runtime value) and the part beyond `depth` is
             // skipped.  A thread issues ALL of its loads of the step (22 per operand) before its first
@@ -1030,7 +1045,7 @@ __device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm,
                     if (bk < depth) sm->b[bk][bc] = vb[u];
                 }
             }
-            __syncthreads();
+            worker_sync();
             if (tid < 128) {
 #pragma unroll 8
                 for (int k = 0; k < depth; ++k) {

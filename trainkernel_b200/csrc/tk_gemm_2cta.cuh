@@ -170,7 +170,7 @@ __device__ __forceinline__ void gemm_tc2(Ctx& c, const Params& P, const CUtensor
             }
         }
         __syncwarp();
-    } else {
+    } else if (c.warp < kWorkerWarps) {
         const int quarter = c.warp & 3;
         for (int64_t t = first; t < tiles && !c.aborted(); t += clusters) {
             int tm, tn; pair_coords<GROUP>(t, tiles_m, tiles_n, tm, tn);
@@ -178,9 +178,6 @@ __device__ __forceinline__ void gemm_tc2(Ctx& c, const Params& P, const CUtensor
                 int pm, pn; pair_coords<GROUP>(t + clusters, tiles_m, tiles_n, pm, pn);
                 const int prow = pm * TM + static_cast<int>(rank) * 128 + quarter * 32 + c.lane;
                 if (prow < M && pn * TN < N) Epi::prefetch(P, prow, pn * TN, min(TN, N - pn * TN));
-            }
-            if constexpr (Bg::kActive) {
-                while (!__all_sync(0xffffffffu, mbar_try(&sh->tmem_full[c.acc], c.acc_phase))) { if (!bg_step<Bg>(c, P)) break; }
             }
             if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
             tc_fence_after();

@@ -259,6 +259,9 @@ class FusedShardedTrainingStep:
         device = self.device = flat[0].device
         self.program = insert_gradient_exchange(program, n)
         verbose = options.pop("verbose", False)
+        # with peers, every block gets stream warps: they run the exchange and the FP32 updates of a stage while
+        # the other warps run its GEMM tiles
+        options.setdefault("background", self.world > 1)
         inplace = {1 + n + i: i for i in range(n)}
         # The size of the symmetric buffer depends on the exchange form, and whether the multicast form
         # is available is only known once a buffer has been mapped: plan both, allocate for the larger.
