@@ -739,7 +739,9 @@ class _Emitter:
             bg = "tk::NoBg"
             if background:
                 bg = f"Bg_{stage}"
-                runs, totals = [], []
+                if len(background) > 8:
+                    raise ValueError("trainkernel: more than 8 background units in one stage")
+                runs, setup = [], []
                 for k, unit in enumerate(background):
                     fn = _Body()
                     fn.depth = 1
@@ -750,15 +752,21 @@ class _Emitter:
                     self.functors.append(f"// {unit.name} ({unit.kind}) of stage {stage}, one 32-thread slice of item `it`\n"
                                          f"static __device__ __noinline__ void bg_{stage}_{k}(const Params& P, tk::Ctx& c, int64_t it, int tid) {{\n{fn.text()}\n}}\n")
                     b0, n = bases[id(unit)], unit.items
-                    totals.append(f"tk::owned_items({b0}LL, {n}LL)")
-                    runs.append(f"        {{ const int64_t n = tk::owned_items({b0}LL, {n}LL) * {THREADS // 32}; if (o < n) {{ bg_{stage}_{k}(P, c, tk::first_item({b0}LL) + (o / {THREADS // 32}) * gridDim.x, "
-                                f"(int)(o % {THREADS // 32}) * 32 + lane); return; }} o -= n; }}")
+                    setup.append(f"if (threadIdx.x == {k}) {{ shared_state.bg_count[{k}] = (int)tk::owned_items({b0}LL, {n}LL) * {THREADS // 32}; "
+                                 f"shared_state.bg_first[{k}] = (int)tk::first_item({b0}LL); }}")
+                    runs.append(f"        {{ const int n = c.sh->bg_count[{k}]; if (o < n) {{ bg_{stage}_{k}(P, c, (int64_t)c.sh->bg_first[{k}] + (int64_t)(o / {THREADS // 32}) * gridDim.x, "
+                                f"(o % {THREADS // 32}) * 32 + lane); return; }} o -= n; }}")
+                # a piece is one 32-thread slice of one of this block's items; the per-unit counts are worked out once per
+                # stage, so that handing out a piece costs a shared-memory atomic and a few 32-bit operations
                 self.functors.append(
                     f"struct Bg_{stage} {{\n    static constexpr bool kActive = true;\n"
-                    f"    static __device__ __forceinline__ int total() {{ return (int)({THREADS // 32} * ({' + '.join(totals)})); }}\n"
-                    f"    static __device__ __forceinline__ void run(const Params& P, tk::Ctx& c, int ordinal, int lane) {{\n        int64_t o = ordinal;\n"
+                    f"    static __device__ __forceinline__ void run(const Params& P, tk::Ctx& c, int ordinal, int lane) {{\n        int o = ordinal;\n"
                     + "\n".join(runs) + "\n    }\n};\n")
-                body.emit(f"if (threadIdx.x == 0) {{ shared_state.bg_next = shared_state.bg_back = shared_state.bg_taken = 0; shared_state.bg_total = {bg}::total(); }}")
+                for line in setup:
+                    body.emit(line)
+                body.emit("__syncthreads();")
+                total = " + ".join(f"shared_state.bg_count[{k}]" for k in range(len(background)))
+                body.emit(f"if (threadIdx.x == 0) {{ shared_state.bg_next = shared_state.bg_back = shared_state.bg_taken = 0; shared_state.bg_total = {total}; }}")
                 body.emit("__syncthreads();")
             foreground = [u for u in ordered if u not in background]
             if self.background and foreground:

@@ -151,6 +151,8 @@ struct SharedState {
     int bg_back;          // ... and from its back
     int bg_taken;         // pieces handed out so far (front and back together)
     int bg_total;         // number of background pieces this block owns in the current stage
+    int bg_count[8];      // per background unit of the stage: pieces this block owns
+    int bg_first[8];      // ... and the first of its items that belongs to this block
     float reduce[32];
 };
 

@@ -52,6 +52,59 @@ def stage_profile(fn: Callable[..., Any], example_inputs: Sequence[Any], *, trai
     return records
 
 
+def sharded_stage_profile(sizes, batch: int, *, repeats: int = 5, seed: int = 0, **options: Any) -> list[dict] | None:
+    """Per-stage times of the batch-sharded one-kernel step, over ALL ranks (run under torchrun, NCCL group up).
+
+    Every rank runs the step with stage stamps and gathers, per stage of its fastest launch: the stage's
+    duration, the time block 0 then spent waiting for its peers' flags (`peer_wait`), and the grid
+    barrier's skew and release times.  Rank 0 returns one record per stage with the maximum and minimum
+    over ranks (a stage is as slow as its slowest rank; the spread is rank skew), the other ranks None.
+    """
+    import torch.distributed as dist
+
+    from . import dp, workloads
+    rank, world = dist.get_rank(), dist.get_world_size()
+    device = torch.device("cuda", torch.cuda.current_device())
+    work = workloads.mlp_workload("sharded", tuple(sizes), batch, seed=seed, device=device, rows=dp.shard_rows(batch, rank, world))
+    step = dp.FusedShardedTrainingStep(work.fn(), (work.state, *work.batches[0]), stage_stamps=True, **options)
+    checker = step._checker
+    stages = step.generated.stages
+    best = None
+    for i in range(3 + repeats):
+        step(work.state, *work.batches[i % len(work.batches)])
+        stamps = checker.stage_stamps()
+        stalls = checker.barrier_stalls()
+        total = stamps[-1] - stamps[0]
+        if i >= 3 and (best is None or total < best[0]):
+            best = (total, [b - a for a, b in zip(stamps[:-1], stamps[1:])], stalls)
+    step.status()
+    total, durations, stalls = best
+    row = torch.zeros(stages, 4, dtype=torch.float64, device=device)
+    for s in range(stages):
+        row[s, 0] = durations[s]
+        if s < len(stalls):
+            row[s, 1], row[s, 2] = stalls[s]["skew"], stalls[s]["release"]
+        if s > 0 and s - 1 < len(stalls):
+            row[s, 3] = stalls[s - 1]["peer_wait"]
+    gathered = [torch.zeros_like(row) for _ in range(world)]
+    dist.all_gather(gathered, row)
+    units = step.generated.units
+    multicast = step.multicast
+    step.close()
+    dist.barrier()
+    if rank != 0:
+        return None
+    table = torch.stack(gathered)                     # [rank, stage, figure]
+    records = []
+    for s in range(stages):
+        records.append({"stage": s, "max_us": float(table[:, s, 0].max()) / 1e3, "min_us": float(table[:, s, 0].min()) / 1e3,
+                        "peer_wait_max_us": float(table[:, s, 3].max()) / 1e3, "barrier_skew_max_us": float(table[:, s, 1].max()) / 1e3,
+                        "barrier_release_max_us": float(table[:, s, 2].max()) / 1e3,
+                        "units": [f"{name}:{kind}{'/' + path if path else ''}x{items}" for st, kind, name, path, items in units if st == s]})
+    records.append({"world": world, "multicast": multicast, "sum_max_us": sum(r["max_us"] for r in records)})
+    return records
+
+
 def main(argv=None) -> int:
     """`python -m trainkernel_b200.profile c4` prints the stage table of a named workload as JSON lines.
 
@@ -65,12 +118,33 @@ def main(argv=None) -> int:
 
     parser = argparse.ArgumentParser(description=main.__doc__)
     parser.add_argument("workload", choices=workloads.CONFIG_NAMES)
+    parser.add_argument("--sharded", action="store_true",
+                        help="c5 only, under torchrun: the batch-sharded one-kernel step, per-stage maximum over ranks")
+    parser.add_argument("--no-stream-warps", action="store_true")
+    parser.add_argument("--no-multicast", action="store_true")
     parser.add_argument("--repeats", type=int, default=10)
     parser.add_argument("--plain", action="store_true")
     parser.add_argument("--device", default="cuda:0")
     parser.add_argument("--trace-stage", type=int, default=None,
                         help="also time the roles of the first single-CTA tensor-core tile of this stage")
     args = parser.parse_args(argv)
+    if args.sharded:
+        import os
+
+        import torch.distributed as dist
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        sizes, batch = ((4096, 8192, 8192, 8192, 4096), 8192) if args.workload == "c5" else ((1024, 2048, 2048, 1024), 512)
+        options = {"background": not args.no_stream_warps}
+        if args.no_multicast:
+            options["multicast"] = False
+        records = sharded_stage_profile(sizes, batch, repeats=args.repeats, **options)
+        for record in records or []:
+            print(json.dumps(record), flush=True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+        return 0
     work = workloads.build(args.workload, device=args.device)
     inputs = (work.state, *work.batches[0])
     if args.plain:
