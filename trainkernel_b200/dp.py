@@ -237,6 +237,11 @@ class FusedShardedTrainingStep:
     # switch for the issuing rank's own copy) and its loads are not hidden behind a GEMM; measured on
     # two B200s the scatter form is 8 % faster per step.
     MULTICAST_FROM = 4
+    # Smallest world size at which every block gets stream warps (four more warps that run the exchange and the
+    # FP32 updates of a stage beside its GEMM tiles).  Measured on B200 with the medium MLP: at four ranks the
+    # step takes 2.75 ms with them and 3.12 ms without; at two ranks, where the GEMM stages are twice as long
+    # and the GPUs run at their power limit, 4.67 ms with them and 4.58 ms without.
+    STREAM_WARPS_FROM = 4
 
     def __init__(self, fn: Callable[..., Any], example_inputs: Sequence[Any], *, group: Any = None,
                  multicast: bool | None = None, health: PeerHealth | None = None, **options: Any) -> None:
@@ -261,7 +266,7 @@ class FusedShardedTrainingStep:
         verbose = options.pop("verbose", False)
         # with peers, every block gets stream warps: they run the exchange and the FP32 updates of a stage while
         # the other warps run its GEMM tiles
-        options.setdefault("background", self.world > 1)
+        options.setdefault("background", self.world >= self.STREAM_WARPS_FROM)
         inplace = {1 + n + i: i for i in range(n)}
         # The size of the symmetric buffer depends on the exchange form, and whether the multicast form
         # is available is only known once a buffer has been mapped: plan both, allocate for the larger.
