@@ -138,7 +138,13 @@ def main(argv=None) -> int:
         options = {"background": not args.no_stream_warps}
         if args.no_multicast:
             options["multicast"] = False
-        records = sharded_stage_profile(sizes, batch, repeats=args.repeats, **options)
+        try:
+            records = sharded_stage_profile(sizes, batch, repeats=args.repeats, **options)
+        except BaseException as error:          # a rank that dies must not leave its peers waiting in a collective
+            import os
+            import sys
+            print(f"[profile] rank {dist.get_rank()} failed: {error!r}", file=sys.stderr, flush=True)
+            os._exit(1)
         for record in records or []:
             print(json.dumps(record), flush=True)
         torch.cuda.synchronize()
