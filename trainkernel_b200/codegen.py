@@ -210,11 +210,8 @@ class _Emitter:
             if cache_key in env:
                 return env[cache_key]
             name = body.temp("l")
-            address = self._affine(access.offset, access.strides, coords, False)
-            step = access.strides[vdim] if access.strides else 0
             body.emit(self._decl(name, width))
-            loader = "ld_row_stream" if access.buffer in self.state_inputs and access.dtype == "float32" else "ld_row_strided"
-            body.emit(f"{self._row_loop()}tk::{loader}<{width}>({self.pointer(access.buffer, access.dtype, True)} + ({address}), {step}LL, {nvalid}, {name}{self._row});")
+            self._emit_load(access, body, name, width, coords, nvalid, vdim)
             env[cache_key] = name
             env[key] = name
             return name
@@ -232,6 +229,13 @@ class _Emitter:
         body.emit(f"{self._loop(width)} {name}{self._at} = {ROUND[op.output.dtype]}::rnd({formula});")
         env[key] = name
         return name
+
+    def _emit_load(self, access: Access, body: _Body, name: str, width: str, coords: list[str], nvalid: str, vdim: int = -1) -> None:
+        """`width` consecutive elements (along dim `vdim`) of a stored value at `coords`, into array `name`."""
+        address = self._affine(access.offset, access.strides, coords, False)
+        step = access.strides[vdim] if access.strides else 0
+        loader = "ld_row_stream" if access.buffer in self.state_inputs and access.dtype == "float32" else "ld_row_strided"
+        body.emit(f"{self._row_loop()}tk::{loader}<{width}>({self.pointer(access.buffer, access.dtype, True)} + ({address}), {step}LL, {nvalid}, {name}{self._row});")
 
     @staticmethod
     def formula(op: Operation, a: list[str]) -> str:
@@ -306,13 +310,36 @@ class _Emitter:
         """
         op = unit.root
         name = f"Epi_{unit.name}"
-        body = _Body()
-        body.depth = 2
-        env: dict = {}
+        # every stored value the epilogue reads, in a fixed order: fetched by `load_rows`, consumed by `run_rows`
+        operands: list[Access] = []
+
+        def gather(expr) -> None:
+            if isinstance(expr, Load):
+                if expr.access not in operands:
+                    operands.append(expr.access)
+            elif isinstance(expr, Apply):
+                for arg in expr.args:
+                    gather(arg)
+
+        if unit.bias is not None:
+            gather(unit.bias)
+        for expr in unit.exprs.values():
+            gather(expr)
         self.rows = True
         coords = ["(x0 + r * rs)", "x1"]
+        mask = f"_Pragma(\"unroll\") for (int r = 0; r < R; ++r) nv[r] = (x0 + r * rs < {unit.mnk[0]}) ? nvalid : 0;"
+        fetch = _Body()
+        fetch.depth = 2
+        fetch.emit("int nv[R];")
+        fetch.emit(mask)
+        env: dict = {}
+        for i, access in enumerate(operands):
+            self._emit_load(access, fetch, f"L.l{i}", "W", coords, "nv[r]")
+            env[("load", access)] = f"L.l{i}"
+        body = _Body()
+        body.depth = 2
         body.emit("int nv[R];")
-        body.emit(f"_Pragma(\"unroll\") for (int r = 0; r < R; ++r) nv[r] = (x0 + r * rs < {unit.mnk[0]}) ? nvalid : 0;")
+        body.emit(mask)
         root = body.temp("v")
         rounding = ROUND[op.output.dtype]
         if op.op == "addmm":
@@ -338,33 +365,30 @@ class _Emitter:
         self.rows = False
         partials = {f.scratch for f in unit.fused}
         wide = any(ELEMENT_BYTES[s.dtype] == 4 for s in unit.stores if s.buffer not in partials)
-        # tile-shaped operands the epilogue reads (same row/column as the accumulator): worth prefetching into L2
-        fetched: list[Access] = []
-
-        def collect(expr) -> None:
-            if isinstance(expr, Load):
-                a = expr.access
-                if a.strides[0] != 0 and a.strides[1] == 1 and a not in fetched:
-                    fetched.append(a)
-            elif isinstance(expr, Apply):
-                for arg in expr.args:
-                    collect(arg)
-
-        for expr in unit.exprs.values():
-            collect(expr)
-        if unit.bias is not None:
-            collect(unit.bias)
+        # tile-shaped operands (same row/column as the accumulator): worth prefetching into L2 a tile ahead
+        fetched = [a for a in operands if a.strides[0] != 0 and a.strides[1] == 1]
         prefetch = "".join(
             f"        tk::prefetch_l2({self.pointer(a.buffer, a.dtype, True)} + ({a.offset}LL + (int64_t)row * {a.strides[0]}LL + col0), ncols * {ELEMENT_BYTES[a.dtype]});\n"
             for a in fetched)
+        # The tensor-core epilogue keeps the operands of the NEXT 32-column chunk in flight while it works on the
+        # current one; each operand costs 32 registers per chunk, so only epilogues with few operands do it.
+        pipelined = 0 < len(operands) <= (1 if self.threads > THREADS else 2)
+        fields = " ".join(f"float l{i}[R][W];" for i in range(len(operands)))
         self.functors.append(
             f"struct {name} {{\n"
             f"    static constexpr bool kWide = {'true' if wide else 'false'};   // stores FP32 tiles: prefer 4-column runs\n"
-            f"    template <int R, int W> static __device__ __forceinline__ void run_rows(const Params& P, int x0, int rs, int x1, int nvalid, const float (*acc)[W]) {{\n"
+            f"    static constexpr bool kPipelined = {'true' if pipelined else 'false'};   // fetch a chunk's operands one chunk ahead\n"
+            f"    template <int R, int W> struct Ops {{ {fields} }};   // what the epilogue reads for R runs of W columns\n"
+            f"    template <int R, int W> static __device__ __forceinline__ void load_rows(const Params& P, int x0, int rs, int x1, int nvalid, Ops<R, W>& L) {{\n"
+            f"{fetch.text()}\n"
+            f"    }}\n"
+            f"    template <int R, int W> static __device__ __forceinline__ void run_rows(const Params& P, int x0, int rs, int x1, int nvalid, const float (*acc)[W], const Ops<R, W>& L) {{\n"
             f"{body.text()}\n"
             f"    }}\n"
             f"    template <int W> static __device__ __forceinline__ void run(const Params& P, int x0, int x1, int nvalid, const float* acc) {{\n"
-            f"        run_rows<1, W>(P, x0, 0, x1, nvalid, reinterpret_cast<const float (*)[W]>(acc));\n"
+            f"        Ops<1, W> L;\n"
+            f"        load_rows<1, W>(P, x0, 0, x1, nvalid, L);\n"
+            f"        run_rows<1, W>(P, x0, 0, x1, nvalid, reinterpret_cast<const float (*)[W]>(acc), L);\n"
             f"    }}\n"
             f"    static __device__ __forceinline__ void prefetch(const Params& P, int row, int col0, int ncols) {{\n"
             f"{prefetch}"

@@ -839,8 +839,28 @@ __device__ __forceinline__ int64_t owned_items(int64_t base, int64_t n) {
 constexpr int kEpiPitch = 36;                       // floats per staged row: 16-byte aligned, conflict-free
 struct alignas(16) EpiStage { float t[kEpiThreads / 32][32][kEpiPitch]; };
 
+// Operands of one chunk in the layout the warp will consume them in (see epilogue_chunk).
+template <typename Epi>
+struct EpiOps {
+    using type = typename std::conditional<Epi::kWide, typename Epi::template Ops<8, 4>, typename Epi::template Ops<4, 8>>::type;
+};
+
+// Issue the global loads of the chunk at (row0, col0): called one chunk ahead of epilogue_chunk, so that the
+// loads are in flight while the previous chunk's accumulator is read, transposed, combined and stored.
 template <typename Epi, typename Params>
-__device__ __forceinline__ void epilogue_chunk(Ctx& c, const Params& P, const float* acc, int row0, int col0, int ncols) {
+__device__ __forceinline__ void epilogue_fetch(Ctx& c, const Params& P, int row0, int col0, int ncols, typename EpiOps<Epi>::type& L) {
+    if constexpr (Epi::kWide) {
+        const int cq = (c.lane & 7) * 4, rq = c.lane >> 3;
+        Epi::template load_rows<8, 4>(P, row0 + rq, 4, col0 + cq, max(0, min(4, ncols - cq)), L);
+    } else {
+        const int cq = (c.lane & 3) * 8, rq = c.lane >> 2;
+        Epi::template load_rows<4, 8>(P, row0 + rq, 8, col0 + cq, max(0, min(8, ncols - cq)), L);
+    }
+}
+
+template <typename Epi, typename Params>
+__device__ __forceinline__ void epilogue_chunk(Ctx& c, const Params& P, const float* acc, int row0, int col0, int ncols,
+                                               const typename EpiOps<Epi>::type& L) {
     float* stage = c.epi + (c.warp - 2) * 32 * kEpiPitch;
     float* mine = stage + c.lane * kEpiPitch;
 #pragma unroll
@@ -854,7 +874,7 @@ __device__ __forceinline__ void epilogue_chunk(Ctx& c, const Params& P, const fl
             const float4 q = *reinterpret_cast<const float4*>(stage + (rq + 4 * r) * kEpiPitch + cq);
             v[r][0] = q.x; v[r][1] = q.y; v[r][2] = q.z; v[r][3] = q.w;
         }
-        Epi::template run_rows<8, 4>(P, row0 + rq, 4, col0 + cq, max(0, min(4, ncols - cq)), v);
+        Epi::template run_rows<8, 4>(P, row0 + rq, 4, col0 + cq, max(0, min(4, ncols - cq)), v, L);
     } else {
         const int cq = (c.lane & 3) * 8, rq = c.lane >> 2;      // runs of 8 columns, rows rq, rq+8, ...
         float v[4][8];
@@ -865,9 +885,42 @@ __device__ __forceinline__ void epilogue_chunk(Ctx& c, const Params& P, const fl
             v[r][0] = q0.x; v[r][1] = q0.y; v[r][2] = q0.z; v[r][3] = q0.w;
             v[r][4] = q1.x; v[r][5] = q1.y; v[r][6] = q1.z; v[r][7] = q1.w;
         }
-        Epi::template run_rows<4, 8>(P, row0 + rq, 8, col0 + cq, max(0, min(8, ncols - cq)), v);
+        Epi::template run_rows<4, 8>(P, row0 + rq, 8, col0 + cq, max(0, min(8, ncols - cq)), v, L);
     }
     __syncwarp();
+}
+
+// The epilogue of one accumulator tile of TN columns starting at tile column `tile_col0`: 32-column chunks, two per
+// iteration so that the operand buffers alternate without run-time indexing.  With Epi::kPipelined the operands
+// of chunk i + 1 are requested before chunk i is read out of TMEM; `first` must then already hold chunk 0's.
+template <int TN, typename Epi, typename Params>
+__device__ __forceinline__ void epilogue_tile(Ctx& c, const Params& P, uint32_t taddr, int row0, int tile_col0, int N,
+                                              typename EpiOps<Epi>::type& first) {
+    typename EpiOps<Epi>::type second;
+#pragma unroll 1
+    for (int cc = 0; cc < TN; cc += 64) {
+        const int col0 = tile_col0 + cc;
+        if (col0 >= N) break;                              // warp-uniform
+        const bool pair = col0 + 32 < N;
+        if constexpr (Epi::kPipelined) {
+            if (pair) epilogue_fetch<Epi>(c, P, row0, col0 + 32, min(32, N - col0 - 32), second);
+        } else {
+            epilogue_fetch<Epi>(c, P, row0, col0, min(32, N - col0), first);
+        }
+        float acc[32];
+        tc_ld32(taddr + cc, acc);
+        tc_wait_ld();
+        epilogue_chunk<Epi>(c, P, acc, row0, col0, min(32, N - col0), first);
+        if (!pair) break;
+        if constexpr (Epi::kPipelined) {
+            if (cc + 64 < TN && col0 + 64 < N) epilogue_fetch<Epi>(c, P, row0, col0 + 64, min(32, N - col0 - 64), first);
+        } else {
+            epilogue_fetch<Epi>(c, P, row0, col0 + 32, min(32, N - col0 - 32), second);
+        }
+        tc_ld32(taddr + cc + 32, acc);
+        tc_wait_ld();
+        epilogue_chunk<Epi>(c, P, acc, row0, col0 + 32, min(32, N - col0 - 32), second);
+    }
 }
 
 // ----------------------------------------------------------------------------
@@ -973,20 +1026,14 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
                 const int prow = pm * BM + quarter * 32 + c.lane;
                 if (prow < M && pn * BN < N) Epi::prefetch(P, prow, pn * BN, min(BN, N - pn * BN));
             }
+            const int row0 = tm * BM + quarter * 32;
+            typename EpiOps<Epi>::type operands;
+            if constexpr (Epi::kPipelined) epilogue_fetch<Epi>(c, P, row0, tn * BN, min(32, N - tn * BN), operands);   // in flight during the wait
             if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
             tc_fence_after();
             if (threadIdx.x == 64) TK_TRACE(4, t);
-            const int row0 = tm * BM + quarter * 32;
             const uint32_t taddr = c.tmem + c.acc * kMaxBN + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-            for (int cc = 0; cc < BN; cc += 32) {
-                const int col0 = tn * BN + cc;
-                if (col0 >= N) break;                  // warp-uniform
-                float acc[32];
-                tc_ld32(taddr + cc, acc);
-                tc_wait_ld();
-                epilogue_chunk<Epi>(c, P, acc, row0, col0, min(32, N - col0));
-            }
+            epilogue_tile<BN, Epi>(c, P, taddr, row0, tn * BN, N, operands);
             tc_fence_before();
             __syncwarp();
             if (c.lane == 0) mbar_arrive(&sh->tmem_empty[c.acc]);

@@ -179,19 +179,13 @@ __device__ __forceinline__ void gemm_tc2(Ctx& c, const Params& P, const CUtensor
                 const int prow = pm * TM + static_cast<int>(rank) * 128 + quarter * 32 + c.lane;
                 if (prow < M && pn * TN < N) Epi::prefetch(P, prow, pn * TN, min(TN, N - pn * TN));
             }
+            const int row0 = tm * TM + static_cast<int>(rank) * 128 + quarter * 32;
+            typename EpiOps<Epi>::type operands;
+            if constexpr (Epi::kPipelined) epilogue_fetch<Epi>(c, P, row0, tn * TN, min(32, N - tn * TN), operands);   // in flight during the wait
             if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
             tc_fence_after();
-            const int row0 = tm * TM + static_cast<int>(rank) * 128 + quarter * 32;
             const uint32_t taddr = c.tmem + c.acc * kMaxBN + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-            for (int cc = 0; cc < TN; cc += 32) {
-                const int col0 = tn * TN + cc;
-                if (col0 >= N) break;
-                float acc[32];
-                tc_ld32(taddr + cc, acc);
-                tc_wait_ld();
-                epilogue_chunk<Epi>(c, P, acc, row0, col0, min(32, N - col0));
-            }
+            epilogue_tile<TN, Epi>(c, P, taddr, row0, tn * TN, N, operands);
             tc_fence_before();
             __syncwarp();
             if (c.lane == 0) {
