@@ -121,6 +121,7 @@ class _Emitter:
         self.needs_simt = False
         self.raster_group = 8
         self.trace_stage = None
+        self.epilogue_lookahead = True
         self.rows = False
         self.background = plan.background
         self.threads = THREADS + (32 * STREAM_WARPS if plan.background else 0)
@@ -372,7 +373,7 @@ class _Emitter:
             for a in fetched)
         # The tensor-core epilogue keeps the operands of the NEXT 32-column chunk in flight while it works on the
         # current one; each operand costs 32 registers per chunk, so only epilogues with few operands do it.
-        pipelined = 0 < len(operands) <= (1 if self.threads > THREADS else 2)
+        pipelined = self.epilogue_lookahead and 0 < len(operands) <= (1 if self.threads > THREADS else 2)
         fields = " ".join(f"float l{i}[R][W];" for i in range(len(operands)))
         self.functors.append(
             f"struct {name} {{\n"
@@ -958,7 +959,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
              two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
              multicast: bool = False, cluster_barrier: bool | None = None, trace_stage: int | None = None,
-             carry_shadows: bool | str | None = None, **reference_knobs) -> GeneratedKernel:
+             carry_shadows: bool | str | None = None, epilogue_lookahead: bool = True, **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -995,6 +996,9 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     `"reorder"` keeps one and orders its rewrite behind its last reader, `False` casts in every
     launch.  A module with carried values must not be launched on two streams at once.
 
+    `epilogue_lookahead` (default on): tensor-core epilogues that read at most two stored operands
+    request the operands of the next 32-column chunk before they read the current chunk out of TMEM.
+
     With `world > 1` the kernel takes `1 + world` extra inputs after the program's own: this rank's
     symmetric buffer, then every rank's mapping of it in rank order.  `multicast=True` adds one more,
     this rank's pointer to the NVSwitch multicast mapping of the buffer, and exchanges through
@@ -1025,6 +1029,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
             raise ValueError("trainkernel: the symmetric buffer's header has no room for this many ranks")
     emitter = _Emitter(plan)
     emitter.trace_stage = trace_stage
+    emitter.epilogue_lookahead = bool(epilogue_lookahead)
     if raster_group is not None:
         if type(raster_group) is not int or not 1 <= raster_group <= 64:
             raise ValueError("trainkernel: raster_group must be between 1 and 64")
