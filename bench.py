@@ -528,14 +528,15 @@ def main() -> None:
         elapsed_ms = begin.elapsed_time(end)
         # further replays only for the latency distribution: 10 warm-ups, then `--latency-replays` timed ones
         samples = [elapsed_ms / steps * 1e3]
-        for i in range(10 + max(0, args.latency_replays - 1)):
+        settle = 10 if args.latency_replays > 1 else 0       # --latency-replays 1: profiler runs, as few launches as possible
+        for i in range(settle + max(0, args.latency_replays - 1)):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             barrier()
             a.record()
             graph.replay()
             b.record()
             barrier()
-            if i >= 10:
+            if i >= settle:
                 samples.append(a.elapsed_time(b) / steps * 1e3)
     status()
     clocks = sampler.summary()

@@ -105,6 +105,15 @@ int tk_module_set_cluster(tk_module* module, int size);
  * are always cooperative (trainkernel/codegen.py:886). */
 int tk_module_set_cooperative(tk_module* module, int enabled);
 
+/* Launch with (1) or without (0, the default) programmatic stream serialisation: the kernel may then START
+ * while its predecessor on the stream is still finishing, and sets up what needs no memory (barriers in
+ * shared memory, tensor memory, tensor-map prefetch) before it waits, inside the kernel
+ * (`griddepcontrol.wait`), for the predecessor to complete and its writes to be visible.  The generated
+ * kernels always contain that wait, which does nothing in an ordinary launch.  It takes the launch latency
+ * and the prologue of a step off the critical path of back-to-back steps (a CUDA graph of steps, an eager
+ * loop).  No counterpart in the reference (trainkernel/codegen.py:886). */
+int tk_module_set_early_launch(tk_module* module, int enabled);
+
 /* Largest grid a cooperative launch of this kernel accepts on its device. */
 int tk_module_max_coresident_blocks(tk_module* module, int* out);
 

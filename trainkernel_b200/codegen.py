@@ -870,6 +870,10 @@ class _Emitter:
             entry.append("    c.epi = &epi_stage.t[0][0][0];")
         if n_maps_used:
             entry.append(f"    if (threadIdx.x < {n_maps_used}) tk::tma_prefetch_desc(&P.maps[threadIdx.x]);")
+        # Everything above touched only shared memory, tensor memory and the parameter block.  From here on the
+        # kernel reads what earlier work on the stream wrote: wait for it (a no-op unless launched early).
+        entry.append("    tk::launch_dependents();")
+        entry.append("    tk::dependency_wait();")
         if exchanging:
             entry.append(f"    tk::dp_init(c.dp, const_cast<void*>(P.in[{len(plan.program.inputs)}]));")
         if plan.carry_bytes:

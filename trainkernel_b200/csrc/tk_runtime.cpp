@@ -117,6 +117,7 @@ struct tk_module {
     int blocks_per_sm = 0;
     int cluster = 1;
     std::atomic<int> cooperative{1};
+    std::atomic<int> early_launch{0};  // launch with programmatic stream serialisation (the kernel waits for its predecessor itself)
     // Encoded tensor maps of recent launches, kMapWays per map slot keyed by base address: a caller that
     // cycles through a few resident batches or double buffers (the common case in an eager loop) does not
     // pay for re-encoding them.
@@ -288,7 +289,7 @@ int tk_module_launch_flags(tk_module* m, const void* const* inputs, void* const*
     }
     memcpy(cursor + 44, &flags, 4);
 
-    CUlaunchAttribute attribute[2];
+    CUlaunchAttribute attribute[3];
     memset(attribute, 0, sizeof(attribute));
     unsigned attributes = 0;
     if (m->cooperative.load()) {
@@ -300,6 +301,11 @@ int tk_module_launch_flags(tk_module* m, const void* const* inputs, void* const*
         attribute[attributes].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
         attribute[attributes].value.clusterDim.x = static_cast<unsigned>(m->cluster);
         attribute[attributes].value.clusterDim.y = attribute[attributes].value.clusterDim.z = 1;
+        ++attributes;
+    }
+    if (m->early_launch.load()) {
+        attribute[attributes].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attribute[attributes].value.programmaticStreamSerializationAllowed = 1;
         ++attributes;
     }
     CUlaunchConfig config;
@@ -372,6 +378,12 @@ int tk_module_set_cluster(tk_module* m, int size) {
 int tk_module_set_cooperative(tk_module* m, int enabled) {
     if (!m) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_set_cooperative");
     m->cooperative.store(enabled ? 1 : 0);
+    return 0;
+}
+
+int tk_module_set_early_launch(tk_module* m, int enabled) {
+    if (!m) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_set_early_launch");
+    m->early_launch.store(enabled ? 1 : 0);
     return 0;
 }
 

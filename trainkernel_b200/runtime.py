@@ -105,6 +105,7 @@ def library() -> ctypes.CDLL:
         lib.tk_module_stage_stamps.argtypes = [p, p, ctypes.POINTER(u64), i32]
         lib.tk_module_set_cluster.argtypes = [p, i32]
         lib.tk_module_set_cooperative.argtypes = [p, i32]
+        lib.tk_module_set_early_launch.argtypes = [p, i32]
         lib.tk_module_unload.argtypes = [p]
         lib.tk_module_unload.restype = None
         _library = lib
