@@ -249,6 +249,36 @@ def run(args) -> dict:
     return result
 
 
+HELDOUT_SEEDS = (101, 211, 307)
+HELDOUT_SHAPES = {"tiny-online": (4, 32, 64, 16), "online": (1, 128, 128, 16), "small": (32, 128, 256, 64), "medium": (128, 512, 1024, 256)}
+
+
+def heldout_suite(args) -> dict:
+    """The reference's held-out protocol (reference: docs/a100-methodology.md:34-42,
+    scripts/run_train_loop_suite.sh:7-28): the four harness shapes, each on three seeds that took no part in
+    choosing any option, `--samples` paired samples per run; per shape and method the figure reported is the
+    MEDIAN OF THE THREE SEED MEDIANS (microseconds per step), with every seed's median and the pass/fail of its
+    trajectory and replay checks beside it."""
+    summary: dict = {"status": "ok", "seeds": list(HELDOUT_SEEDS), "samples": args.samples, "shapes": {}}
+    for shape, (batch, input_size, hidden, output) in HELDOUT_SHAPES.items():
+        per_seed = {}
+        for seed in HELDOUT_SEEDS:
+            one = argparse.Namespace(**{**vars(args), "batch": batch, "input": input_size, "hidden": hidden, "output": output,
+                                        "seed": seed, "json": None})
+            result = run(one)
+            if result["status"] != "ok":
+                summary["status"] = "error"
+            per_seed[seed] = {"status": result["status"],
+                              "median_us_per_step": {n: t["median_ms"] * 1e3 for n, t in result.get("timings", {}).items()}}
+        methods = sorted({n for r in per_seed.values() for n in r["median_us_per_step"]})
+        summary["shapes"][shape] = {
+            "batch_input_hidden_output": [batch, input_size, hidden, output],
+            "median_of_seed_medians_us": {n: sorted(r["median_us_per_step"].get(n, float("nan")) for r in per_seed.values())[len(per_seed) // 2]
+                                          for n in methods},
+            "per_seed": per_seed}
+    return summary
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--batch", type=int, default=128)
@@ -264,12 +294,14 @@ def main(argv=None) -> int:
     parser.add_argument("--task", choices=("regression", "classification-head"), default="regression")
     parser.add_argument("--max-blocks", type=int, default=None)
     parser.add_argument("--json", type=Path)
+    parser.add_argument("--heldout", action="store_true",
+                        help="run the four harness shapes on the three held-out seeds and report the median of the seed medians")
     args = parser.parse_args(argv)
     counts = (args.batch, args.input, args.hidden, args.output, args.batches, args.steps, args.trajectory_steps, args.warmup, args.samples)
     if any(value < 1 for value in counts):
         parser.error("all sizes and iteration counts must be positive")
     try:
-        result = run(args)
+        result = heldout_suite(args) if args.heldout else run(args)
     except Exception as exc:  # the JSON records the failure, as the harness is run unattended
         import traceback
         result = {"status": "error", "error": f"{type(exc).__name__}: {exc}", "traceback": traceback.format_exc()}

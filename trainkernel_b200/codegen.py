@@ -122,6 +122,7 @@ class _Emitter:
         self.raster_group = 8
         self.trace_stage = None
         self.epilogue_lookahead = True
+        self.stream_piece = 3            # 32-thread slices of a work item that one background piece covers (1, 2, 3 or 6)
         self.rows = False
         self.background = plan.background
         self.threads = THREADS + (32 * STREAM_WARPS if plan.background else 0)
@@ -761,6 +762,8 @@ class _Emitter:
             # other units (the GEMM tiles above all); whoever finishes first helps with what is left.
             background = [u for u in ordered if self.background and not u.carried and
                           (u.kind == "exchange" or (u.kind == "point" and prod(u.dims) and self._flat_ok(u)))]
+            if background and all(u.kind == "point" for u in ordered):
+                background = []      # a stage of nothing but pointwise streams: the plain 192-thread loops move more bytes per second
             bg = "tk::NoBg"
             if background:
                 bg = f"Bg_{stage}"
@@ -777,10 +780,13 @@ class _Emitter:
                     self.functors.append(f"// {unit.name} ({unit.kind}) of stage {stage}, one 32-thread slice of item `it`\n"
                                          f"static __device__ __noinline__ void bg_{stage}_{k}(const Params& P, tk::Ctx& c, int64_t it, int tid) {{\n{fn.text()}\n}}\n")
                     b0, n = bases[id(unit)], unit.items
-                    setup.append(f"if (threadIdx.x == {k}) {{ shared_state.bg_count[{k}] = (int)tk::owned_items({b0}LL, {n}LL) * {THREADS // 32}; "
+                    slices = THREADS // 32                      # 32-thread slices of one item
+                    per_item = slices // self.stream_piece      # pieces an item is cut into
+                    setup.append(f"if (threadIdx.x == {k}) {{ shared_state.bg_count[{k}] = (int)tk::owned_items({b0}LL, {n}LL) * {per_item}; "
                                  f"shared_state.bg_first[{k}] = (int)tk::first_item({b0}LL); }}")
-                    runs.append(f"        {{ const int n = c.sh->bg_count[{k}]; if (o < n) {{ bg_{stage}_{k}(P, c, (int64_t)c.sh->bg_first[{k}] + (int64_t)(o / {THREADS // 32}) * gridDim.x, "
-                                f"(o % {THREADS // 32}) * 32 + lane); return; }} o -= n; }}")
+                    runs.append(f"        {{ const int n = c.sh->bg_count[{k}]; if (o < n) {{ const int64_t it = (int64_t)c.sh->bg_first[{k}] + (int64_t)(o / {per_item}) * gridDim.x; "
+                                f"_Pragma(\"unroll 1\") for (int s = 0; s < {self.stream_piece}; ++s) bg_{stage}_{k}(P, c, it, ((o % {per_item}) * {self.stream_piece} + s) * 32 + lane); "
+                                f"return; }} o -= n; }}")
                 # a piece is one 32-thread slice of one of this block's items; the per-unit counts are worked out once per
                 # stage, so that handing out a piece costs a shared-memory atomic and a few 32-bit operations
                 self.functors.append(
@@ -963,7 +969,8 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
              two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
              multicast: bool = False, cluster_barrier: bool | None = None, trace_stage: int | None = None,
-             carry_shadows: bool | str | None = None, epilogue_lookahead: bool = True, **reference_knobs) -> GeneratedKernel:
+             carry_shadows: bool | str | None = None, epilogue_lookahead: bool = True, stream_piece: int = 3,
+             **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -1000,6 +1007,9 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     `"reorder"` keeps one and orders its rewrite behind its last reader, `False` casts in every
     launch.  A module with carried values must not be launched on two streams at once.
 
+    `stream_piece`: how many 32-thread slices of a work item one background piece covers (a piece is what a
+    stream warp takes from the stage's list at a time; larger pieces cost fewer shared-memory atomics).
+
     `epilogue_lookahead` (default on): tensor-core epilogues that read at most two stored operands
     request the operands of the next 32-column chunk before they read the current chunk out of TMEM.
 
@@ -1034,6 +1044,9 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     emitter = _Emitter(plan)
     emitter.trace_stage = trace_stage
     emitter.epilogue_lookahead = bool(epilogue_lookahead)
+    if stream_piece not in (1, 2, 3, 6):
+        raise ValueError("trainkernel: stream_piece must be 1, 2, 3 or 6")
+    emitter.stream_piece = stream_piece
     if raster_group is not None:
         if type(raster_group) is not int or not 1 <= raster_group <= 64:
             raise ValueError("trainkernel: raster_group must be between 1 and 64")
