@@ -410,6 +410,8 @@ def main() -> None:
     parser.add_argument("--no-stream-warps", action="store_true",
                         help="N > 1, fused: generate the step kernel without the four stream warps per block that run the "
                              "gradient exchange and the FP32 updates beside the GEMM tiles (for A/B measurements)")
+    parser.add_argument("--stream-everything", action="store_true",
+                        help="N > 1, fused: give every pointwise stream to the stream warps, whether the stage's GEMMs cover it or not (A/B measurements)")
     parser.add_argument("--stream-piece", type=int, default=None, help="N > 1, fused: slices per background piece (A/B measurements)")
     parser.add_argument("--no-multicast", action="store_true",
                         help="N > 1, fused: never exchange through the NVSwitch multicast mapping (multimem); "
@@ -456,7 +458,8 @@ def main() -> None:
     elif args.dp == "fused":
         step = dp.FusedShardedTrainingStep(work.fn(), (state, x0, t0), multicast=False if args.no_multicast else None,
                                            **({"background": False} if args.no_stream_warps else {}),
-                                           **({"stream_piece": args.stream_piece} if args.stream_piece else {}))
+                                           **({"stream_piece": args.stream_piece} if args.stream_piece else {}),
+                                           **({"stream_everything": True} if args.stream_everything else {}))
         kernels_per_step = step.kernels_per_step
         status = step.status
         generated = step.generated

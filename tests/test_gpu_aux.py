@@ -254,3 +254,41 @@ def test_carried_weight_copies_follow_every_edit_of_the_state():
         for index, (got, want) in enumerate(zip(state, reference)):
             err = float((got - want).abs().max()) / max(float(want.abs().max()), 1e-30)
             assert err <= tol, f"replay from state x {scale}: parameter {index} is {err:.3e} from the oracle"
+
+
+# ---------------------------------------------------------------------------------------------
+# programmatic dependent launch: a step may start while its predecessor is still finishing
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["c1", "c2", "c3"])
+def test_early_launch_gives_bit_identical_steps(name):
+    """With `tk_module_set_early_launch` a kernel is allowed to start its prologue before the previous
+    kernel on the stream has finished; it waits for it inside the kernel before touching memory.  Twenty
+    back-to-back steps (eager and as a CUDA graph) must leave exactly the state an ordinary launch leaves."""
+    def leaves(state):
+        return tuple(state) if isinstance(state, (tuple, list)) else (state,)
+
+    finals = {}
+    for early in (False, True):
+        work = workloads.build(name, device="cuda")
+        compiled = tk.compile_training(work.fn(), (work.state, *work.batches[0]))
+        assert runtime.library().tk_module_set_early_launch(compiled.runner.module.handle, int(early)) == 0
+        initial = [p.clone() for p in leaves(work.state)]
+        for i in range(20):
+            compiled(work.state, *work.batches[i % len(work.batches)])
+        torch.cuda.synchronize()
+        compiled.runner.status()
+        eager_final = [p.clone() for p in leaves(work.state)]
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(20):
+                compiled(work.state, *work.batches[i % len(work.batches)])
+        for p, saved in zip(leaves(work.state), initial):
+            p.copy_(saved)
+        graph.replay()
+        torch.cuda.synchronize()
+        compiled.runner.status()
+        for a, b in zip(leaves(work.state), eager_final):
+            assert torch.equal(a, b), f"{name}: graph replay differs from the eager loop (early={early})"
+        finals[early] = eager_final
+    for a, b in zip(finals[False], finals[True]):
+        assert torch.equal(a, b), f"{name}: early launch changed the result"

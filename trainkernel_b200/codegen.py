@@ -20,6 +20,8 @@ from math import prod
 from .ir import Operation, Program, TensorSpec, row_major, validate
 from .plan import (ELEMENT_BYTES, SYM_HEADER, THREADS, Access, Apply, Const, Iota, Load, Plan, Planner, Ref, Unit, point_unroll)
 
+TENSOR_RATE = 1.4e15             # flop/s the planner assumes for tensor-core GEMM tiles when it balances a stage
+STREAM_RATE = 5.0e12             # bytes/s it assumes for a pointwise stream run by the worker warps
 STREAM_WARPS = 4                 # tk::kStreamWarps: extra warps of a kernel generated with background=True
 MAX_STAMPED_STAGES = 55          # stamp area: 64 words per table, the peer-wait table shares its block with the role trace
 FLAG_WORDS_PER_RANK = 64         # cross-rank "passed barrier k" words per rank in the symmetric header
@@ -122,6 +124,7 @@ class _Emitter:
         self.raster_group = 8
         self.trace_stage = None
         self.epilogue_lookahead = True
+        self.stream_everything = False   # A/B switch: every flat pointwise stream goes to the stream warps, covered or not
         self.stream_piece = 3            # 32-thread slices of a work item that one background piece covers (1, 2, 3 or 6)
         self.rows = False
         self.background = plan.background
@@ -760,10 +763,24 @@ class _Emitter:
             # Memory-bound units (gradient exchange, flat pointwise streams such as the FP32 updates) of a kernel
             # with stream warps: warps 6..9 of every block work through them while warps 0..5 run the stage's
             # other units (the GEMM tiles above all); whoever finishes first helps with what is left.
-            background = [u for u in ordered if self.background and not u.carried and
-                          (u.kind == "exchange" or (u.kind == "point" and prod(u.dims) and self._flat_ok(u)))]
-            if background and all(u.kind == "point" for u in ordered):
-                background = []      # a stage of nothing but pointwise streams: the plain 192-thread loops move more bytes per second
+            # Exchanges always go to the stream warps.  A pointwise stream goes there only while the stage's GEMM
+            # tiles last long enough to cover it: pieces handed out 32 threads at a time move fewer bytes per second
+            # than the plain 192-thread loop (measured 3.3 against 4.9 TB/s for an FP32 update), so a stream that
+            # the tensor work cannot hide is run by the worker warps, after their tiles, while the stream warps
+            # carry the stage's exchange.
+            background = []
+            if self.background:
+                tensor_seconds = sum(2.0 * prod(u.mnk) for u in ordered if u.kind == "gemm" and u.path in ("tc", "tc2")) / TENSOR_RATE
+                for unit in ordered:
+                    if unit.carried:
+                        continue
+                    if unit.kind == "exchange":
+                        background.append(unit)
+                    elif unit.kind == "point" and prod(unit.dims) and self._flat_ok(unit):
+                        seconds = sum(prod(plan.shapes[b]) * ELEMENT_BYTES[plan.dtypes[b]] for b in unit.reads | unit.writes) / STREAM_RATE
+                        if seconds <= tensor_seconds or self.stream_everything:
+                            tensor_seconds -= seconds
+                            background.append(unit)
             bg = "tk::NoBg"
             if background:
                 bg = f"Bg_{stage}"
@@ -970,7 +987,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
              multicast: bool = False, cluster_barrier: bool | None = None, trace_stage: int | None = None,
              carry_shadows: bool | str | None = None, epilogue_lookahead: bool = True, stream_piece: int = 3,
-             **reference_knobs) -> GeneratedKernel:
+             stream_everything: bool = False, **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -1047,6 +1064,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     if stream_piece not in (1, 2, 3, 6):
         raise ValueError("trainkernel: stream_piece must be 1, 2, 3 or 6")
     emitter.stream_piece = stream_piece
+    emitter.stream_everything = bool(stream_everything)
     if raster_group is not None:
         if type(raster_group) is not int or not 1 <= raster_group <= 64:
             raise ValueError("trainkernel: raster_group must be between 1 and 64")
