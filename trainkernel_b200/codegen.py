@@ -945,7 +945,7 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
                  fuse_epilogues: bool = True, max_blocks: int | None = None, tensor_cores: bool = True,
                  block_n: int | None = None, two_cta: bool | None = None, world: int = 1,
                  background: bool = False, multicast: bool = False, cluster_barrier: bool | None = None,
-                 carry_shadows: bool | str | None = None) -> Plan:
+                 carry_shadows: bool | str | None = None, wave_aware_tiles: bool = False) -> Plan:
     """Validate, canonicalise and plan `program` (no code is emitted)."""
     validate(program)
     from .passes import canonicalize_transposed_mm
@@ -974,7 +974,8 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
             raise ValueError("trainkernel: inplace outputs must be computed values, not input views")
     return Planner(program, inplace_outputs=mapping, fuse_pointwise=fuse_pointwise, fuse_epilogues=fuse_epilogues,
                    max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n, two_cta=two_cta, world=world,
-                   background=background, multicast=multicast, cluster_barrier=cluster_barrier, carry=carry_shadows).plan()
+                   background=background, multicast=multicast, cluster_barrier=cluster_barrier, carry=carry_shadows,
+                   wave_aware_tiles=wave_aware_tiles).plan()
 
 
 _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shared_skew", "split_k_gemv",
@@ -987,7 +988,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
              multicast: bool = False, cluster_barrier: bool | None = None, trace_stage: int | None = None,
              carry_shadows: bool | str | None = None, epilogue_lookahead: bool = True, stream_piece: int = 3,
-             stream_everything: bool = False, **reference_knobs) -> GeneratedKernel:
+             stream_everything: bool = False, wave_aware_tiles: bool = False, **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -1046,7 +1047,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     plan = plan_program(program, inplace_outputs=inplace_outputs, fuse_pointwise=fuse_pointwise,
                         fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n,
                         two_cta=two_cta, world=world, background=background, multicast=multicast,
-                        cluster_barrier=cluster_barrier, carry_shadows=carry_shadows)
+                        cluster_barrier=cluster_barrier, carry_shadows=carry_shadows, wave_aware_tiles=wave_aware_tiles)
     # Fixed-size tables the kernel indexes by stage or barrier number: the stamp area, and (with peers) the
     # 64 flag words per rank in the symmetric buffer's header, laid out from word 16.
     if stage_stamps and plan.stages > MAX_STAMPED_STAGES:

@@ -207,8 +207,10 @@ class Planner:
     def __init__(self, program: Program, *, inplace_outputs: dict[int, int] | None = None,
                  fuse_pointwise: bool = True, fuse_epilogues: bool = True, max_blocks: int | None = None,
                  tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None, world: int = 1, background: bool = False,
-                 multicast: bool = False, cluster_barrier: bool | None = None, carry: bool | str | None = None):
+                 multicast: bool = False, cluster_barrier: bool | None = None, carry: bool | str | None = None,
+                 wave_aware_tiles: bool = False):
         self.program = program
+        self.wave_aware_tiles = wave_aware_tiles
         if carry not in (None, True, False, "pingpong", "reorder"):
             raise ValueError("trainkernel: carry_shadows must be None, True, False, 'pingpong' or 'reorder'")
         self.carry = "pingpong" if carry is True else carry
@@ -1041,7 +1043,15 @@ class Planner:
             if unit.path == "tc":
                 tiles_m = -(-m // 128)
                 choice = self.forced_block_n
-                if choice is None:
+                if choice is None and self.wave_aware_tiles:
+                    # A mid-size GEMM's main loop is bound by what an SM pulls from L2 per K block, (128 + BN) rows of
+                    # 128 bytes, and its tiles run in waves of one per SM: take the width with the least waves x bytes.
+                    # (An experiment, off by default: on the small MLP it gives the dW GEMMs one 128 x 128 or 128 x 256
+                    # tile per block instead of two or four narrow ones, and the step got SLOWER, 144 against 134 us,
+                    # because a block with a single tile cannot overlap its epilogue with a next main loop.)
+                    choice = min((64, 128, 256), key=lambda bn: (-(-(tiles_m * -(-n // bn)) // SM_COUNT) * (128 + bn), bn))
+                    choice = min(choice, max(64, -(-n // 64) * 64))
+                elif choice is None:
                     choice = 64
                     for bn in (256, 128):
                         if tiles_m * -(-n // bn) >= SM_COUNT:
