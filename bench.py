@@ -221,7 +221,8 @@ def run_reference(args) -> None:
         "impl": "reference", "metric": "captured_step_throughput", "value": base["value"], "unit": "steps/s",
         "n_gpus": args.gpus, "steps": timed, "warmup": 1, "ms_per_step": 1e3 / base["value"],
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": _config(args.workload, args.gpus, MEDIUM_BATCH // max(1, args.gpus), 4, None, 0),
+        "config": _config(args.workload, args.gpus, MEDIUM_BATCH // max(1, args.gpus), 4),
+        "execution": {"how": "IR-interpreter oracle on CPU tensors, all host threads, rank 0 only", "graph_steps": 0},
         "requested": {"steps": args.steps, "warmup": args.warmup,
                       "note": "a CPU step takes seconds: at most 3 whole steps are timed after a 256-row warm-up"},
         "cpu_baseline": base,
@@ -231,16 +232,14 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
-def _config(workload: str, world: int, rows_per_rank: int, resident: int, parallelism: str | None, graph_steps: int) -> dict:
-    """The `config` object, built the same way by both arms so that they describe the same workload."""
+def _config(workload: str, world: int, rows_per_rank: int, resident: int) -> dict:
+    """The `config` object: what the workload IS, built the same way by both arms so that the two lines carry
+    equal objects; how an arm executes it (parallelism, graph length) goes under `execution`."""
     config = {"workload": _workload_text(workload), "global_batch": MEDIUM_BATCH, "rows_per_rank": rows_per_rank,
               "resident_batches": resident,
               "l2": "inputs larger than L2 (FP32 weights %d MB, %d MB per batch)" % (
                   sum(a * b for a, b in zip(MEDIUM_SIZES[:-1], MEDIUM_SIZES[1:])) * 4 // 2**20,
                   rows_per_rank * (MEDIUM_SIZES[0] + MEDIUM_SIZES[-1]) * 2 // 2**20)}
-    if parallelism is not None:
-        config["parallelism"] = parallelism
-        config["graph_steps"] = graph_steps
     return config
 
 
@@ -597,7 +596,8 @@ def main() -> None:
         "metric": "captured_step_throughput", "value": steps / (elapsed_ms * 1e-3), "unit": "steps/s",
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": elapsed_ms / steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": _config(args.workload, world, work.batch, len(work.batches), parallelism, 0 if args.eager else steps),
+        "config": _config(args.workload, world, work.batch, len(work.batches)),
+        "execution": {"parallelism": parallelism, "graph_steps": 0 if args.eager else steps},
         "latency_us": _percentiles(samples),
         "clocks": clocks, "roofline": roofline, "e2e": e2e,
         "gpu_launches": steps * kernels_per_step,
