@@ -152,11 +152,13 @@ class Unit:
 def point_unroll(total: int, streams: int = 2) -> int:
     """Independent 8-element chunks each thread of a flat pointwise unit keeps in flight per iteration.
 
-    Large streams need ~48 KiB in flight per SM to cover HBM latency (8 chunks x 192 threads x 32 B);
-    small ones keep more blocks busy with less unrolling.
+    Large streams need ~50 KiB of LOADS in flight per SM to cover HBM latency at full bandwidth: 8 chunks x
+    192 threads x 32 B for a one-input stream; 6 chunks for units with more tensors per element (an FP32
+    update reads a master and a mean, 48 B per chunk: 6 x 192 x 48 B = 54 KiB; with 4 chunks it measured
+    4.9 of 6.5 TB/s).  Small streams keep more blocks busy with less unrolling.
     """
     if total >= SM_COUNT * THREADS * 8 * 8:
-        return 8 if streams <= 2 else 4          # more tensors per element: fewer chunks, same bytes in flight
+        return 8 if streams <= 2 else 6
     if total >= SM_COUNT * THREADS * 8 * 2:
         return 2
     return 1
