@@ -293,3 +293,46 @@ def test_loss_and_bias_gradient_sums_are_formed_in_gemm_epilogues():
     # without epilogue fusion the reductions read their operands from memory again
     unfused = plan_program(program, inplace_outputs=inplace, fuse_epilogues=False)
     assert any(u.kind == "reduce" and u.phase == "partial" for u in unfused.units)
+
+
+def test_weight_copies_are_carried_only_in_kernels_of_large_gemms():
+    program, inplace = _medium_program()
+    plan = plan_program(program, inplace_outputs=inplace)
+    assert plan.two_cta and plan.carry_pingpong and plan.carry_bytes == 2 * 2 * 201326592
+    carried = [u for u in plan.units if u.carried]
+    assert len(carried) == 4 and all(u.stage == 0 and u.kind == "point" for u in carried)
+    for unit in carried:                                   # read copy and written copy swap places with the phase word
+        copy = unit.members[0].output.buffer
+        read, written = plan.storage[copy], plan.storage[copy + "__next"]
+        assert read[0] == written[0] == "carry" and (read[1], read[2]) == (written[2], written[1]) and read[1] != read[2]
+    # the schedule is the one without carrying: dW and dX of a layer still share a stage
+    plain = plan_program(program, inplace_outputs=inplace, carry_shadows=False)
+    assert [(u.name, u.stage) for u in plan.units if u.kind == "gemm"] == [(u.name, u.stage) for u in plain.units if u.kind == "gemm"]
+    small, small_inplace = _step_program("c4")
+    assert plan_program(small, inplace_outputs=small_inplace).carry_bytes == 0
+    with pytest.raises(ValueError, match="carry_shadows"):
+        plan_program(small, inplace_outputs=small_inplace, carry_shadows="sometimes")
+
+
+def test_stream_warps_take_exchanges_and_only_the_updates_the_gemms_cover():
+    import re
+    from trainkernel_b200.passes import insert_gradient_exchange
+    program, inplace = _medium_program(batch=1024)          # one of eight ranks
+    exchanged = insert_gradient_exchange(program, 8)
+    g = generate(exchanged, inplace_outputs=inplace, world=8, multicast=True, background=True)
+    assert g.threads == 320 and "c.warp < tk::kWorkerWarps" in g.source and "bar.sync" not in g.source
+    pieces = re.findall(r"// (\S+) \((\w+)\) of stage (\d+), one 32-thread slice", g.source)
+    exchanges = {name for _, kind, name, _, _ in g.units if kind == "exchange"}
+    assert {name for name, kind, _ in pieces if kind == "exchange"} == exchanges      # every exchange runs in the stream warps
+    stage_of = {name: stage for stage, _, name, _, _ in g.units}
+    gemm_stages = {stage for stage, kind, _, path, _ in g.units if kind == "gemm"}
+    streamed_updates = [name for name, kind, _ in pieces if kind == "point"]
+    assert streamed_updates and all(stage_of[name] in gemm_stages for name in streamed_updates)
+    # the two large updates of the tail (8192 x 8192 masters) find no GEMM long enough: plain loops by the worker warps
+    large = [name for stage, kind, name, _, items in g.units if kind == "point" and items > 7000]
+    assert len(large) == 2 and not set(large) & set(streamed_updates)
+    everything = generate(exchanged, inplace_outputs=inplace, world=8, multicast=True, background=True, stream_everything=True)
+    assert set(large) <= {name for name, kind, _ in re.findall(r"// (\S+) \((\w+)\) of stage (\d+), one 32-thread slice", everything.source)}
+    # without stream warps the kernel has 192 threads and no background pieces
+    plain = generate(exchanged, inplace_outputs=inplace, world=8, multicast=True)
+    assert plain.threads == 192 and "32-thread slice" not in plain.source
