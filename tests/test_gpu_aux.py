@@ -194,7 +194,8 @@ def _oracle_step(program, state, batch):
     return out, tuple(e.clone() for e in out[1 + n:])
 
 
-def test_carried_weight_copies_follow_every_edit_of_the_state():
+@pytest.mark.parametrize("form", ["pingpong", "reorder"])
+def test_carried_weight_copies_follow_every_edit_of_the_state(form):
     """The step kernel keeps the BF16 copies of its master weights between launches and skips re-casting them
     when the state tensors are untouched.  Every way of touching them must still give the oracle's result:
     an in-place PyTorch operation (seen through the version counter), a write PyTorch cannot see followed by
@@ -202,9 +203,10 @@ def test_carried_weight_copies_follow_every_edit_of_the_state():
     tol = REL_TOL[torch.bfloat16]
     work = workloads.build("c4", device="cuda")
     cpu_program, _ = tk.capture(work.fn(), (work.state, *work.batches[0]))
-    compiled = tk.compile_training(work.fn(), (work.state, *work.batches[0]), stage_stamps=True, carry_shadows=True)
+    compiled = tk.compile_training(work.fn(), (work.state, *work.batches[0]), stage_stamps=True, carry_shadows=form)
     runner = compiled.runner
-    assert runner.generated.carry_bytes == 2 * 2 * work.weight_elements and runner.carried is not None
+    copies = 2 if form == "pingpong" else 1
+    assert runner.generated.carry_bytes == copies * 2 * work.weight_elements and runner.carried is not None
     state = work.state
     reference = tuple(p.clone() for p in state)
     first_stage = []
