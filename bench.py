@@ -89,7 +89,7 @@ def kernel_sources() -> dict[str, str]:
         for multicast in (False, True):
             name = f"medium_fused_n{world}" + ("_multicast" if multicast else "")
             sources[name] = codegen.generate(fused, inplace_outputs={1 + count + i: i for i in range(count)}, world=world,
-                                             multicast=multicast, background=world >= 4).source
+                                             multicast=multicast, background=multicast or world >= 4).source
     return sources
 
 
@@ -409,6 +409,8 @@ def main() -> None:
     parser.add_argument("--no-stream-warps", action="store_true",
                         help="N > 1, fused: generate the step kernel without the four stream warps per block that run the "
                              "gradient exchange and the FP32 updates beside the GEMM tiles (for A/B measurements)")
+    parser.add_argument("--stream-warps", action="store_true", help="N > 1, fused: stream warps even below the rank count they default from (A/B measurements)")
+    parser.add_argument("--multicast", action="store_true", help="N > 1, fused: require the NVSwitch multicast form even below the rank count it defaults from")
     parser.add_argument("--stream-everything", action="store_true",
                         help="N > 1, fused: give every pointwise stream to the stream warps, whether the stage's GEMMs cover it or not (A/B measurements)")
     parser.add_argument("--stream-piece", type=int, default=None, help="N > 1, fused: slices per background piece (A/B measurements)")
@@ -455,8 +457,8 @@ def main() -> None:
             # should the blocks not all be resident after all, give up on a barrier after 0.2 s instead of 2 s
             runtime.library().tk_module_set_timeout(step.runner.module.handle, 200_000_000)
     elif args.dp == "fused":
-        step = dp.FusedShardedTrainingStep(work.fn(), (state, x0, t0), multicast=False if args.no_multicast else None,
-                                           **({"background": False} if args.no_stream_warps else {}),
+        step = dp.FusedShardedTrainingStep(work.fn(), (state, x0, t0), multicast=False if args.no_multicast else (True if args.multicast else None),
+                                           **({"background": False} if args.no_stream_warps else ({"background": True} if args.stream_warps else {})),
                                            **({"stream_piece": args.stream_piece} if args.stream_piece else {}),
                                            **({"stream_everything": True} if args.stream_everything else {}))
         kernels_per_step = step.kernels_per_step

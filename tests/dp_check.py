@@ -139,7 +139,7 @@ def kernel_sources() -> dict[str, str]:
             program = _meta_program(sizes, batch // world)
             for multicast in (False, True):
                 sources[f"{name}_w{world}_{multicast}"] = codegen.generate(insert_gradient_exchange(program, count), inplace_outputs=inplace,
-                                                                          world=world, multicast=multicast, background=world >= 4).source
+                                                                          world=world, multicast=multicast, background=multicast or world >= 4).source
             gradient, update = split_at_gradients(program, count, narrow_exchange=True)
             sources[f"{name}_w{world}_gradient"] = codegen.generate(gradient).source
             sources[f"{name}_w{world}_update"] = codegen.generate(update, inplace_outputs={count + i: i for i in range(count)}).source

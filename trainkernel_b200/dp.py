@@ -234,13 +234,14 @@ class FusedShardedTrainingStep:
 
     # Smallest world size at which the multicast form is preferred when available.  With two ranks it
     # moves more bytes per link than scattering does (every multimem access also loops through the
-    # switch for the issuing rank's own copy) and its loads are not hidden behind a GEMM; measured on
-    # two B200s the scatter form is 8 % faster per step.
-    MULTICAST_FROM = 4
-    # Smallest world size at which every block gets stream warps (four more warps that run the exchange and the
-    # FP32 updates of a stage beside its GEMM tiles).  Measured on B200 with the medium MLP: at four ranks the
-    # step takes 2.75 ms with them and 3.12 ms without; at two ranks, where the GEMM stages are twice as long
-    # and the GPUs run at their power limit, 4.67 ms with them and 4.58 ms without.
+    # switch for the issuing rank's own copy), but with stream warps issuing its loads beside the GEMM
+    # tiles it is the faster form there too: measured on two B200s, one call, ms per step: multicast with
+    # stream warps 4.30, peer stores without 4.43, peer stores with 4.50, multicast without 4.81.
+    MULTICAST_FROM = 2
+    # Smallest world size at which every block of the PEER-STORE form gets stream warps (four more warps that run
+    # the exchange and the FP32 updates of a stage beside its GEMM tiles); the multicast form always has them.
+    # Measured on B200 with the medium MLP: at four ranks the step takes 2.75 ms with them and 3.12 ms without;
+    # at two ranks the peer-store form takes 4.50 ms with them and 4.43 ms without.
     STREAM_WARPS_FROM = 4
 
     def __init__(self, fn: Callable[..., Any], example_inputs: Sequence[Any], *, group: Any = None,
@@ -266,17 +267,24 @@ class FusedShardedTrainingStep:
         verbose = options.pop("verbose", False)
         # with peers, every block gets stream warps: they run the exchange and the FP32 updates of a stage while
         # the other warps run its GEMM tiles
-        options.setdefault("background", self.world >= self.STREAM_WARPS_FROM)
+        asked = options.pop("background", None)
+
+        def stream_warps(through_the_switch: bool) -> bool:
+            if asked is not None:
+                return bool(asked)
+            return self.world > 1 if through_the_switch else self.world >= self.STREAM_WARPS_FROM
+
         inplace = {1 + n + i: i for i in range(n)}
         # The size of the symmetric buffer depends on the exchange form, and whether the multicast form
         # is available is only known once a buffer has been mapped: plan both, allocate for the larger.
-        self.generated = generate(self.program, inplace_outputs=inplace, world=self.world, **options)
+        self.generated = generate(self.program, inplace_outputs=inplace, world=self.world, background=stream_warps(False), **options)
         words = self.generated.symmetric_bytes // 4
         through_switch = None
         if multicast is None:
             multicast = None if self.world >= self.MULTICAST_FROM else False
         if self.world > 1 and multicast is not False:
-            through_switch = generate(self.program, inplace_outputs=inplace, world=self.world, multicast=True, **options)
+            through_switch = generate(self.program, inplace_outputs=inplace, world=self.world, multicast=True,
+                                      background=stream_warps(True), **options)
             words = max(words, through_switch.symmetric_bytes // 4)
         # the peer-mapped buffer: header words (epoch, rank, barrier flags) then the exchanged values
         if self.world > 1:
