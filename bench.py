@@ -411,6 +411,7 @@ def main() -> None:
                              "gradient exchange and the FP32 updates beside the GEMM tiles (for A/B measurements)")
     parser.add_argument("--stream-warps", action="store_true", help="N > 1, fused: stream warps even below the rank count they default from (A/B measurements)")
     parser.add_argument("--multicast", action="store_true", help="N > 1, fused: require the NVSwitch multicast form even below the rank count it defaults from")
+    parser.add_argument("--exchange-chunks", type=int, default=None, help="N > 1, fused: owned chunks per exchange work item, 8 or 16 (A/B measurements)")
     parser.add_argument("--stream-everything", action="store_true",
                         help="N > 1, fused: give every pointwise stream to the stream warps, whether the stage's GEMMs cover it or not (A/B measurements)")
     parser.add_argument("--stream-piece", type=int, default=None, help="N > 1, fused: slices per background piece (A/B measurements)")
@@ -460,7 +461,8 @@ def main() -> None:
         step = dp.FusedShardedTrainingStep(work.fn(), (state, x0, t0), multicast=False if args.no_multicast else (True if args.multicast else None),
                                            **({"background": False} if args.no_stream_warps else ({"background": True} if args.stream_warps else {})),
                                            **({"stream_piece": args.stream_piece} if args.stream_piece else {}),
-                                           **({"stream_everything": True} if args.stream_everything else {}))
+                                           **({"stream_everything": True} if args.stream_everything else {}),
+                                           **({"exchange_chunks": args.exchange_chunks} if args.exchange_chunks else {}))
         kernels_per_step = step.kernels_per_step
         status = step.status
         generated = step.generated

@@ -857,6 +857,8 @@ class _Emitter:
         use_tc = "true" if plan.uses_tc else "false"
         widest = max((u.block_n for u in plan.units if u.kind == "gemm" and u.path == "tc"), default=256)
         ring = ([] if plan.two_cta else [f"#define TK_RING_BN {64 if widest <= 64 else 128 if widest <= 128 else 256}"])
+        if plan.symmetric_bytes:
+            ring = ring + [f"#define TK_EXCHANGE_CHUNKS {plan.exchange_chunks}"]
         header = ring + ([f"#define TK_TRACE_STAGE {int(self.trace_stage)}"] if self.trace_stage is not None else []) + [
             '#include "tk_gemm_2cta.cuh"' if plan.two_cta else '#include "tk_device.cuh"',
             "struct Params {",
@@ -945,7 +947,8 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
                  fuse_epilogues: bool = True, max_blocks: int | None = None, tensor_cores: bool = True,
                  block_n: int | None = None, two_cta: bool | None = None, world: int = 1,
                  background: bool = False, multicast: bool = False, cluster_barrier: bool | None = None,
-                 carry_shadows: bool | str | None = None, wave_aware_tiles: bool = False) -> Plan:
+                 carry_shadows: bool | str | None = None, wave_aware_tiles: bool = False,
+                 exchange_chunks: int = 8) -> Plan:
     """Validate, canonicalise and plan `program` (no code is emitted)."""
     validate(program)
     from .passes import canonicalize_transposed_mm
@@ -975,7 +978,7 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
     return Planner(program, inplace_outputs=mapping, fuse_pointwise=fuse_pointwise, fuse_epilogues=fuse_epilogues,
                    max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n, two_cta=two_cta, world=world,
                    background=background, multicast=multicast, cluster_barrier=cluster_barrier, carry=carry_shadows,
-                   wave_aware_tiles=wave_aware_tiles).plan()
+                   wave_aware_tiles=wave_aware_tiles, exchange_chunks=exchange_chunks).plan()
 
 
 _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shared_skew", "split_k_gemv",
@@ -988,7 +991,8 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
              multicast: bool = False, cluster_barrier: bool | None = None, trace_stage: int | None = None,
              carry_shadows: bool | str | None = None, epilogue_lookahead: bool = True, stream_piece: int = 3,
-             stream_everything: bool = False, wave_aware_tiles: bool = False, **reference_knobs) -> GeneratedKernel:
+             stream_everything: bool = False, wave_aware_tiles: bool = False, exchange_chunks: int = 8,
+             **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -1047,7 +1051,8 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     plan = plan_program(program, inplace_outputs=inplace_outputs, fuse_pointwise=fuse_pointwise,
                         fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n,
                         two_cta=two_cta, world=world, background=background, multicast=multicast,
-                        cluster_barrier=cluster_barrier, carry_shadows=carry_shadows, wave_aware_tiles=wave_aware_tiles)
+                        cluster_barrier=cluster_barrier, carry_shadows=carry_shadows, wave_aware_tiles=wave_aware_tiles,
+                        exchange_chunks=exchange_chunks)
     # Fixed-size tables the kernel indexes by stage or barrier number: the stamp area, and (with peers) the
     # 64 flag words per rank in the symmetric buffer's header, laid out from word 16.
     if stage_stamps and plan.stages > MAX_STAMPED_STAGES:

@@ -642,12 +642,17 @@ __device__ __forceinline__ void st_row_scatter(const void* const* peers, uint64_
     }
 }
 
-constexpr int kExchangeChunksPerItem = 8;
+// Owned chunks one exchange work item covers = 16-byte loads each thread keeps in flight through the switch.
+// A generated kernel defines TK_EXCHANGE_CHUNKS to what its planner cut the items for.
+#ifndef TK_EXCHANGE_CHUNKS
+#define TK_EXCHANGE_CHUNKS 8
+#endif
+constexpr int kExchangeChunksPerItem = TK_EXCHANGE_CHUNKS;
 
 // Mean over ranks of a dense value, rounded to T: chunk c (THREADS x 16 bytes) is reduced by rank
 // c % WORLD, which reads every rank's contribution from its own staging area (filled by
 // st_row_scatter; fixed order, FP32 sum), scales by 1/WORLD, rounds, and stores the result into
-// every rank's result region.  Every rank ends up with the bit-identical mean.  One item = 8 owned chunks.
+// every rank's result region.  Every rank ends up with the bit-identical mean.  One item = kExchangeChunksPerItem owned chunks.
 template <typename R, int WORLD>
 __device__ __noinline__ void exchange_mean_item(const Dp& d, const void* const* peers, uint64_t src_offset, uint64_t owned_bytes,
                                                    uint64_t dst_offset, int64_t numel, int64_t it, int tid) {
@@ -756,26 +761,30 @@ __device__ __noinline__ void exchange_mean_mc_item(const Dp& d, const void* cons
     const int64_t chunks = (numel + chunk - 1) / chunk;
     const float scale = 1.0f / static_cast<float>(WORLD);
     char* base = reinterpret_cast<char*>(const_cast<void*>(mc));
+    // This thread's 16 bytes of the item's g-th chunk sit a compile-time stride behind those of chunk 0, so
+    // one 64-bit address and immediates serve all G loads and stores (G 64-bit indices next to G loaded
+    // vectors would not fit the register budget).
+    constexpr int64_t kStride = static_cast<int64_t>(WORLD) * kThreads * VEC;          // elements between owned chunks
+    const int64_t e_first = ((it * G) * WORLD + d.rank) * chunk + static_cast<int64_t>(tid) * VEC;
+    const char* src = base + src_offset + static_cast<uint64_t>(e_first) * sizeof(T);
+    char* dst = base + dst_offset + static_cast<uint64_t>(e_first) * sizeof(T);
     uint4 raw[G];
-    int64_t e0[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+        if (e_first + g * kStride + VEC <= numel) raw[g] = multimem_sum_v4<T>(src + g * kStride * static_cast<int64_t>(sizeof(T)));
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        const int64_t owned = (it * G + g) * WORLD + d.rank;
-        e0[g] = owned < chunks ? owned * chunk + static_cast<int64_t>(tid) * VEC : numel;
-        if (e0[g] + VEC <= numel) raw[g] = multimem_sum_v4<T>(base + src_offset + static_cast<uint64_t>(e0[g]) * sizeof(T));
-    }
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        if (e0[g] >= numel) continue;
-        if (e0[g] + VEC <= numel) {
+        const int64_t e0 = e_first + g * kStride;
+        if (e0 >= numel) continue;
+        if (e0 + VEC <= numel) {
             const T* part = reinterpret_cast<const T*>(&raw[g]);
             uint4 packed;
             T* out = reinterpret_cast<T*>(&packed);
 #pragma unroll
             for (int e = 0; e < VEC; ++e) from_f32(out + e, to_f32(part[e]) * scale);
-            multimem_st_v4(base + dst_offset + static_cast<uint64_t>(e0[g]) * sizeof(T), packed);
+            multimem_st_v4(dst + g * kStride * static_cast<int64_t>(sizeof(T)), packed);
         } else {
-            for (int64_t e = e0[g]; e < numel; ++e) {
+            for (int64_t e = e0; e < numel; ++e) {
                 float sum = 0.0f;
                 for (int j = 0; j < WORLD; ++j)
                     sum += to_f32(ld_volatile<T>(reinterpret_cast<const char*>(peers[j]) + src_offset + e * sizeof(T)));

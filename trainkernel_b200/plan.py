@@ -34,6 +34,11 @@ MAX_CLUSTER = 8                         # portable thread-block cluster size
 CLUSTER_WORK_LIMIT = 30_000_000         # flops-equivalents below which a program runs as one cluster (measured crossover: 9 MF wins, 75 MF loses)
 THREADS = 192
 ALIGN = 256
+# tk::kExchangeChunksPerItem: owned chunks one exchange work item covers = 16-byte loads every thread keeps in
+# flight through the switch.  16 was tried (`exchange_chunks=16`): the item then needs more registers than a
+# called function gets without saving its caller's, and the step was no faster (4 ranks, p50 of 30 replays:
+# 2.81 ms against 2.75 ms with 8).
+EXCHANGE_CHUNKS_PER_ITEM = 8
 
 
 # ---------------------------------------------------------------------------
@@ -203,6 +208,7 @@ class Plan:
     cluster_blocks: int = 0                # > 0: the whole grid is ONE thread-block cluster of this many blocks, stages end in the hardware cluster barrier
     carry_bytes: int = 0                   # size of the buffer that keeps derived values (BF16 weight copies) from one launch to the next
     carry_pingpong: bool = False           # carried values have two copies; a launch reads one and writes the other
+    exchange_chunks: int = 8               # owned chunks per exchange work item (TK_EXCHANGE_CHUNKS of the kernel)
 
 
 class Planner:
@@ -210,8 +216,11 @@ class Planner:
                  fuse_pointwise: bool = True, fuse_epilogues: bool = True, max_blocks: int | None = None,
                  tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None, world: int = 1, background: bool = False,
                  multicast: bool = False, cluster_barrier: bool | None = None, carry: bool | str | None = None,
-                 wave_aware_tiles: bool = False):
+                 wave_aware_tiles: bool = False, exchange_chunks: int = EXCHANGE_CHUNKS_PER_ITEM):
         self.program = program
+        if exchange_chunks not in (8, 16):
+            raise ValueError("trainkernel: exchange_chunks must be 8 or 16")
+        self.exchange_chunks = exchange_chunks
         self.wave_aware_tiles = wave_aware_tiles
         if carry not in (None, True, False, "pingpong", "reorder"):
             raise ValueError("trainkernel: carry_shadows must be None, True, False, 'pingpong' or 'reorder'")
@@ -909,7 +918,7 @@ class Planner:
         return Plan(program, sorted(units, key=lambda u: (u.stage, u.index)), stage_count, storage, dtypes, shapes,
                     max(total, ALIGN), inlined, direct, staged, native, grid, tc_units, tc_units > 0, two_cta,
                     self.world, symmetric if symmetric > SYM_HEADER else 0, tuple(sorted(signal)), self.background, self.multicast, cluster_blocks,
-                    carry_bytes, bool(carry_bytes) and self.carry == "pingpong")
+                    carry_bytes, bool(carry_bytes) and self.carry == "pingpong", self.exchange_chunks)
 
     # -- helpers ---------------------------------------------------------------------
     def _refs(self, expr) -> set[str]:
@@ -1074,10 +1083,10 @@ class Planner:
             else:
                 unit.items = -(-m // 32) * -(-n // 32)
         elif unit.kind == "exchange":
-            # one item = 8 owned chunks of THREADS x 16 bytes; chunk c belongs to rank c % world
+            # one item = EXCHANGE_CHUNKS_PER_ITEM owned chunks of THREADS x 16 bytes; chunk c belongs to rank c % world
             nbytes = prod(unit.dims) * ELEMENT_BYTES[unit.root.output.dtype]
             chunks = -(-nbytes // (THREADS * 16))
-            unit.items = max(1, -(-(-(-chunks // self.world)) // 8))
+            unit.items = max(1, -(-(-(-chunks // self.world)) // self.exchange_chunks))
         elif unit.kind == "reduce":
             outputs = prod(unit.kept)
             if unit.phase == "finish":
