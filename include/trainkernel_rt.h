@@ -85,6 +85,12 @@ int tk_module_device(tk_module* module, int* out);
  * carried values notice that somebody else launched the kernel in between.  No counterpart in the reference. */
 int tk_module_launches(tk_module* module, uint64_t* out);
 int tk_module_set_workspace_bytes(tk_module* module, size_t bytes);
+/* Declares which base pointers the module's kernel accesses with 16-byte vector loads and stores:
+ * `inputs[i]` / `outputs[i]` non-zero for kernel input / output i (arrays may be shorter than the kernel's
+ * lists), `workspace` non-zero for the workspace.  Every later launch returns TK_E_ARGUMENT instead of
+ * launching when one of them is not 16-byte aligned.  Call it once, before the first launch.  No counterpart
+ * in the reference, whose generated kernels use scalar accesses throughout (trainkernel/codegen.py:419-423). */
+int tk_module_require_alignment(tk_module* module, const uint8_t* inputs, int n_inputs, const uint8_t* outputs, int n_outputs, int workspace);
 int tk_module_workspace_bytes(tk_module* module, size_t* out);
 
 /* {registers per thread, local bytes per thread, static + dynamic shared bytes per block,

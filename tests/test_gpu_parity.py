@@ -185,7 +185,9 @@ def test_fused_exchange_step_with_one_rank_matches_oracle_and_replays(stream_war
     work = workloads.build("c2", seed=2, device="cuda")
     cpu = workloads.build("c2", seed=2, device="cpu")
     step = dp.FusedShardedTrainingStep(work.fn(), (work.state, *work.batches[0]), background=stream_warps)
-    assert step.generated.threads == (320 if stream_warps else 192)
+    # 320 threads either way: four stream warps, or without them four more epilogue warps for the tensor-core tiles
+    assert step.generated.threads == 320 and ("32-thread slice" in step.generated.source) == stream_warps
+    assert ("#define TK_EPI_WARPS 8" in step.generated.source) == (not stream_warps)
     assert step.generated.symmetric_bytes > 4096 and "tk::exchange_mean" in step.generated.source
     program, _ = tk.capture(cpu.fn(), (cpu.state, *cpu.batches[0]))
     ref_state = tuple(cpu.state)
@@ -254,3 +256,33 @@ def test_inplace_targets_must_be_detached_from_autograd():
     x = torch.randn(64, device="cuda", requires_grad=True)
     with pytest.raises(ValueError, match="detached|autograd"):
         tk.compile(lambda v: v + 1, (x,), inplace_outputs={0: 0})
+
+
+def test_aligned_kernels_refuse_unaligned_tensors_and_unaligned_examples_keep_the_fallback():
+    """A kernel generated for 16-byte aligned tensors refuses (on the host, before anything is launched) a
+    tensor that is not; compiling on such a tensor drops the assumption, and the step still matches the oracle."""
+    import trainkernel_b200 as tk
+    from oracle import interpreter
+    from trainkernel_b200 import workloads
+    work = workloads.build("c2", seed=5, device="cuda")
+    cpu = workloads.build("c2", seed=5, device="cpu")
+    x, target = work.batches[0]
+    aligned = tk.compile_training(work.fn(), (work.state, x, target))
+    generated = aligned.runner.generated
+    assert generated.aligned_inputs and generated.aligned_outputs and "tk::ld_row_full<" in generated.source
+    shifted = torch.empty(target.numel() + 2, dtype=target.dtype, device="cuda")[2:].view_as(target)   # 4 bytes off
+    shifted.copy_(target)
+    assert shifted.data_ptr() % 16 == 4
+    before = [p.clone() for p in work.state]
+    with pytest.raises(RuntimeError, match="not 16-byte aligned"):
+        aligned(work.state, x, shifted)
+    torch.cuda.synchronize()
+    aligned.runner.status()
+    assert all(torch.equal(a, b) for a, b in zip(before, work.state))          # nothing ran
+    general = tk.compile_training(work.fn(), (work.state, x, shifted))
+    assert not general.runner.generated.aligned_inputs and "_full<" not in general.runner.generated.source
+    program, _ = tk.capture(cpu.fn(), (cpu.state, *cpu.batches[0]))
+    expected = interpreter.run(program, (*cpu.state, *cpu.batches[0]))
+    out = general(work.state, x, shifted)
+    general.runner.status()
+    assert_outputs_close(out, expected, 2e-2, "step on an unaligned target")

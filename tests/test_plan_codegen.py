@@ -34,7 +34,7 @@ def test_tiny_mlp_schedule_shares_stages_and_commits_directly():
     # when asked to, the BF16 copies of W1 and W2 are carried to the next launch in two copies each (read one, write the other)
     carrying = generate(program, inplace_outputs=inplace, carry_shadows=True)
     assert carrying.carry_bytes == 2 * 2 * (128 * 256 + 256 * 128) and carrying.input_count == len(program.inputs) + 1
-    assert carrying.source.count("if (!carried)") == 2 and "tk_carry_phase ?" in carrying.source and carrying.stages == 5
+    assert carrying.source.count("if (!carried") == 2 and "tk_carry_phase ?" in carrying.source and carrying.stages == 5
     # one copy, rewritten in place: dW2 (mm_2), whose epilogue rewrites W2's copy, runs one stage after dX
     # (mm_3), the copy's last reader, and shares that stage with dW1 (mm_4)
     single = generate(program, inplace_outputs=inplace, carry_shadows="reorder")
@@ -336,3 +336,25 @@ def test_stream_warps_take_exchanges_and_only_the_updates_the_gemms_cover():
     # without stream warps the kernel has 192 threads and no background pieces
     plain = generate(exchanged, inplace_outputs=inplace, world=8, multicast=True)
     assert plain.threads == 192 and "32-thread slice" not in plain.source
+
+
+def test_single_cta_tensor_core_kernels_get_eight_epilogue_warps():
+    program, inplace = _step_program("c4")
+    g = generate(program, inplace_outputs=inplace)
+    # 320 threads: warps 6..9 share the TMEM lane quarters of warps 2..5; one ring slot (32 KiB at 128-wide tiles) less
+    assert g.threads == 320 and "#define TK_EPI_WARPS 8" in g.source and "#define TK_RING_BN 128" in g.source
+    assert g.dynamic_smem == 5 * (128 * 64 * 2 + 128 * 64 * 2) + 1024
+    assert "kPipelined = true" not in g.source and "kFetchFirst = true" in g.source     # only the first chunk is fetched early
+    # everything that is not a tensor-core GEMM is cut for 192 threads and keeps the extra warps out
+    assert g.source.count("the four extra epilogue warps have no part in this unit") == sum(
+        1 for _, kind, _, path, _ in g.units if not (kind == "gemm" and path == "tc"))
+    narrow = generate(program, inplace_outputs=inplace, wide_epilogue=False)
+    assert narrow.threads == 192 and "TK_EPI_WARPS" not in narrow.source and narrow.dynamic_smem == 4 * 49152 + 1024
+    assert "kPipelined = true" in narrow.source
+    # pair-tile kernels keep four epilogue warps unless asked; kernels without tensor-core GEMMs have nothing to widen
+    medium, medium_inplace = _medium_program()
+    assert generate(medium, inplace_outputs=medium_inplace).threads == 192
+    asked = generate(medium, inplace_outputs=medium_inplace, wide_epilogue=True)
+    assert asked.threads == 320 and asked.dynamic_smem == 5 * 32768 + 1024
+    plain, plain_inplace = _step_program("c1")
+    assert generate(plain, inplace_outputs=plain_inplace).threads == 192

@@ -88,6 +88,9 @@ class GeneratedKernel:
     multicast: bool = False               # exchanges through the multicast mapping (one more extra input)
     symmetric_bytes: int = 0              # size of the peer-mapped buffer the kernel expects after the program inputs
     carry_bytes: int = 0                  # size of the carry buffer the kernel expects as its LAST input (0: none)
+    aligned_inputs: tuple = ()            # kernel inputs whose base pointer must be 16-byte aligned (the launch refuses others)
+    aligned_outputs: tuple = ()           # likewise for kernel outputs
+    aligned_workspace: bool = False       # likewise for the workspace
 
 
 class _Body:
@@ -128,6 +131,12 @@ class _Emitter:
         self.stream_piece = 3            # 32-thread slices of a work item that one background piece covers (1, 2, 3 or 6)
         self.rows = False
         self.background = plan.background
+        self.wide_epilogue = False       # eight epilogue warps per cta_group::1 GEMM tile instead of four
+        self.assume_aligned = True       # tensor-core epilogues may lean on 16-byte aligned base pointers (checked at launch)
+        self._full_rows = False          # set while the functor of such an epilogue is written
+        self.aligned_inputs: set[int] = set()
+        self.aligned_outputs: set[int] = set()
+        self.aligned_workspace = False
         self.threads = THREADS + (32 * STREAM_WARPS if plan.background else 0)
         exchanging = plan.symmetric_bytes > 0
         # kernel inputs beyond the program's own: [symmetric buffer, every rank's mapping of it, (multicast mapping)], [carry buffer]
@@ -235,10 +244,49 @@ class _Emitter:
         env[key] = name
         return name
 
+    def _aligned_base(self, buffer: str) -> bool:
+        """True when `buffer` starts on a 16-byte boundary, given base pointers that do; records which base
+        pointers the proof leans on (the host checks those at every launch)."""
+        where = self.plan.storage[buffer]
+        if where[0] == "in":
+            self.aligned_inputs.add(where[1])
+        elif where[0] == "out":
+            self.aligned_outputs.add(where[1])
+        elif where[0] == "carry":
+            if where[1] % 16 or where[2] % 16:
+                return False
+            self.aligned_inputs.add(self.carry_input)
+        elif where[0] == "sym":
+            if where[1] % 16:
+                return False
+            self.aligned_inputs.add(len(self.plan.program.inputs))
+        elif where[0] == "scatter":
+            return False
+        else:
+            if where[1] % 16:
+                return False
+            self.aligned_workspace = True
+        return True
+
+    def _full_run(self, buffer: str, dtype: str, offset: int, strides: tuple[int, ...], vdim: int = -1) -> bool:
+        """Inside a tensor-core epilogue whose N is a multiple of 8: can a run of 4 or 8 elements of this access
+        only be wholly valid or wholly invalid, and 16-byte aligned when valid?"""
+        if not self._full_rows or dtype not in ("float32", "bfloat16", "float16") or not strides:
+            return False
+        unit = 16 // ELEMENT_BYTES[dtype]
+        axis = vdim % len(strides)
+        if strides[axis] != 1 or offset % unit or any(stride % unit for d, stride in enumerate(strides) if d != axis):
+            return False
+        return self._aligned_base(buffer)
+
     def _emit_load(self, access: Access, body: _Body, name: str, width: str, coords: list[str], nvalid: str, vdim: int = -1) -> None:
         """`width` consecutive elements (along dim `vdim`) of a stored value at `coords`, into array `name`."""
         address = self._affine(access.offset, access.strides, coords, False)
         step = access.strides[vdim] if access.strides else 0
+        if self._full_run(access.buffer, access.dtype, access.offset, access.strides, vdim):
+            stream = "true" if access.buffer in self.state_inputs and access.dtype == "float32" else "false"
+            body.emit(f"{self._row_loop()}tk::ld_row_full<{width}, {stream}>({self.pointer(access.buffer, access.dtype, True)} + ({address}), {nvalid}, {name}{self._row});")
+            return
         loader = "ld_row_stream" if access.buffer in self.state_inputs and access.dtype == "float32" else "ld_row_strided"
         body.emit(f"{self._row_loop()}tk::{loader}<{width}>({self.pointer(access.buffer, access.dtype, True)} + ({address}), {step}LL, {nvalid}, {name}{self._row});")
 
@@ -302,6 +350,10 @@ class _Emitter:
                 body.emit(f"{self._row_loop()}tk::st_row_scatter<{width}, {self.plan.world}, {CTYPE[store.dtype]}>(&P.in[{n_inputs + 1}], {where[1]}ULL, {where[2]}ULL, "
                           f"reinterpret_cast<const uint32_t*>(P.in[{n_inputs}])[1], {address}, {nvalid}, {env['ref:' + store.buffer]}{self._row});")
                 continue
+            if self._full_run(store.buffer, store.dtype, 0, dense):
+                stream = "true" if store.buffer in self.write_once else "false"
+                body.emit(f"{self._row_loop()}tk::st_row_full<{width}, {stream}>({self.pointer(store.buffer, store.dtype, False)} + ({address}), {nvalid}, {env['ref:' + store.buffer]}{self._row});")
+                continue
             storer = "st_row_stream" if store.buffer in self.write_once else "st_row"
             body.emit(f"{self._row_loop()}tk::{storer}<{width}>({self.pointer(store.buffer, store.dtype, False)} + ({address}), {nvalid}, {env['ref:' + store.buffer]}{self._row});")
 
@@ -331,6 +383,8 @@ class _Emitter:
         for expr in unit.exprs.values():
             gather(expr)
         self.rows = True
+        # N a multiple of 8: every run of 4 or 8 columns a lane handles is wholly inside the tile or wholly outside it
+        self._full_rows = self.assume_aligned and unit.path in ("tc", "tc2") and unit.mnk[1] % 8 == 0
         coords = ["(x0 + r * rs)", "x1"]
         mask = f"_Pragma(\"unroll\") for (int r = 0; r < R; ++r) nv[r] = (x0 + r * rs < {unit.mnk[0]}) ? nvalid : 0;"
         fetch = _Body()
@@ -368,6 +422,7 @@ class _Emitter:
         for fused in unit.fused:
             self._fused_reduce(unit, fused, body, env)
         self.rows = False
+        self._full_rows = False
         partials = {f.scratch for f in unit.fused}
         wide = any(ELEMENT_BYTES[s.dtype] == 4 for s in unit.stores if s.buffer not in partials)
         # tile-shaped operands (same row/column as the accumulator): worth prefetching into L2 a tile ahead
@@ -377,12 +432,14 @@ class _Emitter:
             for a in fetched)
         # The tensor-core epilogue keeps the operands of the NEXT 32-column chunk in flight while it works on the
         # current one; each operand costs 32 registers per chunk, so only epilogues with few operands do it.
-        pipelined = self.epilogue_lookahead and 0 < len(operands) <= (1 if self.threads > THREADS else 2)
+        pipelined = self.epilogue_lookahead is True and 0 < len(operands) <= (1 if self.threads > THREADS else 2)
+        fetch_first = self.epilogue_lookahead == "first" and 0 < len(operands) <= 2
         fields = " ".join(f"float l{i}[R][W];" for i in range(len(operands)))
         self.functors.append(
             f"struct {name} {{\n"
             f"    static constexpr bool kWide = {'true' if wide else 'false'};   // stores FP32 tiles: prefer 4-column runs\n"
             f"    static constexpr bool kPipelined = {'true' if pipelined else 'false'};   // fetch a chunk's operands one chunk ahead\n"
+            f"    static constexpr bool kFetchFirst = {'true' if fetch_first else 'false'};   // fetch the first chunk's operands before waiting for the accumulator\n"
             f"    template <int R, int W> struct Ops {{ {fields} }};   // what the epilogue reads for R runs of W columns\n"
             f"    template <int R, int W> static __device__ __forceinline__ void load_rows(const Params& P, int x0, int rs, int x1, int nvalid, Ops<R, W>& L) {{\n"
             f"{fetch.text()}\n"
@@ -822,13 +879,15 @@ class _Emitter:
                 body.depth += 1
             for unit in foreground:
                 if unit.carried:
-                    body.emit(f"if (!carried) {{   // {unit.name}: skipped when the previous launch left this value behind")
+                    guard = "!carried && c.warp < tk::kWorkerWarps" if self.wide_epilogue else "!carried"
+                    body.emit(f"if ({guard}) {{   // {unit.name}: skipped when the previous launch left this value behind")
                     body.depth += 1
                     self.point(unit, body, bases[id(unit)])
                     body.depth -= 1
                     body.emit("}")
                     continue
-                body.emit("{")
+                workers_only = self.wide_epilogue and not (unit.kind == "gemm" and unit.path in ("tc", "tc2"))
+                body.emit("if (c.warp < tk::kWorkerWarps) {   // the four extra epilogue warps have no part in this unit" if workers_only else "{")
                 body.depth += 1
                 if unit.kind == "exchange":
                     op = unit.root
@@ -857,6 +916,10 @@ class _Emitter:
         use_tc = "true" if plan.uses_tc else "false"
         widest = max((u.block_n for u in plan.units if u.kind == "gemm" and u.path == "tc"), default=256)
         ring = ([] if plan.two_cta else [f"#define TK_RING_BN {64 if widest <= 64 else 128 if widest <= 128 else 256}"])
+        self.ring_bn = 64 if widest <= 64 else 128 if widest <= 128 else 256
+        if self.wide_epilogue:
+            ring = ring + ["#define TK_EPI_WARPS 8"]
+            self.ring_bn = 128 if plan.two_cta else self.ring_bn   # a pair tile's slot holds 128 of the 256 B columns
         if plan.symmetric_bytes:
             ring = ring + [f"#define TK_EXCHANGE_CHUNKS {plan.exchange_chunks}"]
         header = ring + ([f"#define TK_TRACE_STAGE {int(self.trace_stage)}"] if self.trace_stage is not None else []) + [
@@ -948,7 +1011,7 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
                  block_n: int | None = None, two_cta: bool | None = None, world: int = 1,
                  background: bool = False, multicast: bool = False, cluster_barrier: bool | None = None,
                  carry_shadows: bool | str | None = None, wave_aware_tiles: bool = False,
-                 exchange_chunks: int = 8) -> Plan:
+                 exchange_chunks: int = 8, late_casts: bool = False) -> Plan:
     """Validate, canonicalise and plan `program` (no code is emitted)."""
     validate(program)
     from .passes import canonicalize_transposed_mm
@@ -978,7 +1041,7 @@ def plan_program(program: Program, *, inplace_outputs: dict[int, int] | None = N
     return Planner(program, inplace_outputs=mapping, fuse_pointwise=fuse_pointwise, fuse_epilogues=fuse_epilogues,
                    max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n, two_cta=two_cta, world=world,
                    background=background, multicast=multicast, cluster_barrier=cluster_barrier, carry=carry_shadows,
-                   wave_aware_tiles=wave_aware_tiles, exchange_chunks=exchange_chunks).plan()
+                   wave_aware_tiles=wave_aware_tiles, exchange_chunks=exchange_chunks, late_casts=late_casts).plan()
 
 
 _IGNORED_REFERENCE_KNOBS = ("blocks_per_sm", "gemm_k_tile", "gemm_tile_n", "shared_skew", "split_k_gemv",
@@ -990,8 +1053,9 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              tensor_cores: bool = True, block_n: int | None = None, stage_stamps: bool = False,
              two_cta: bool | None = None, raster_group: int | None = None, world: int = 1, background: bool = False,
              multicast: bool = False, cluster_barrier: bool | None = None, trace_stage: int | None = None,
-             carry_shadows: bool | str | None = None, epilogue_lookahead: bool = True, stream_piece: int = 3,
+             carry_shadows: bool | str | None = None, epilogue_lookahead: bool | None = None, stream_piece: int = 3,
              stream_everything: bool = False, wave_aware_tiles: bool = False, exchange_chunks: int = 8,
+             wide_epilogue: bool | None = None, late_casts: bool = False, assume_aligned: bool = True,
              **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
@@ -1032,8 +1096,29 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     `stream_piece`: how many 32-thread slices of a work item one background piece covers (a piece is what a
     stream warp takes from the stage's list at a time; larger pieces cost fewer shared-memory atomics).
 
-    `epilogue_lookahead` (default on): tensor-core epilogues that read at most two stored operands
-    request the operands of the next 32-column chunk before they read the current chunk out of TMEM.
+    `wide_epilogue` (default: on for single-CTA tensor-core kernels, off for pair-tile kernels; never with
+    stream warps): 320 threads per block, eight epilogue warps per accumulator tile instead of four (two per
+    TMEM lane quarter, alternate 32-column chunks), one ring slot less.  Doubles the loads and stores a block
+    keeps in flight while it drains an accumulator, which is what bounds the short-K GEMMs of small programs
+    (8-14 % per step on the small configurations); the K loops of pair-tile kernels hide their epilogues already.
+
+    `assume_aligned` (default on): the epilogue of a tensor-core GEMM whose N is a multiple of 8 reads and
+    writes rows with 16-byte vector accesses only, without the element-wise fallback for ragged or unaligned
+    runs, wherever extents, strides and offsets prove that a run is whole and aligned given 16-byte aligned
+    base pointers; `GeneratedKernel.aligned_inputs` / `aligned_outputs` / `aligned_workspace` name the
+    pointers the proof leans on, and `tk_module_launch` refuses a launch that passes one of them unaligned
+    (compile with `assume_aligned=False` for tensors at odd offsets).  The fallback is a third of an
+    epilogue's instructions; small programs, which fetch every stage's code cold in every launch, run
+    2-11 % faster without it.
+
+    `late_casts`: place a cast of a program input (a BF16 weight copy) in the stage before its first reader
+    instead of the first stage when that stage has tensor-core GEMMs (no measurable difference; off).
+
+    `epilogue_lookahead`: `True` (default with four epilogue warps): tensor-core epilogues that read at most two
+    stored operands request the operands of the next 32-column chunk before they read the current chunk out of
+    TMEM.  `"first"` (default with eight, where the 168-register ceiling of a 320-thread block makes the full form
+    spill): only the first chunk's operands are requested early, before the warp waits for the accumulator.
+    `False`: every chunk loads its operands when it starts.
 
     With `world > 1` the kernel takes `1 + world` extra inputs after the program's own: this rank's
     symmetric buffer, then every rank's mapping of it in rank order.  `multicast=True` adds one more,
@@ -1052,7 +1137,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
                         fuse_epilogues=fuse_epilogues, max_blocks=max_blocks, tensor_cores=tensor_cores, block_n=block_n,
                         two_cta=two_cta, world=world, background=background, multicast=multicast,
                         cluster_barrier=cluster_barrier, carry_shadows=carry_shadows, wave_aware_tiles=wave_aware_tiles,
-                        exchange_chunks=exchange_chunks)
+                        exchange_chunks=exchange_chunks, late_casts=late_casts)
     # Fixed-size tables the kernel indexes by stage or barrier number: the stamp area, and (with peers) the
     # 64 flag words per rank in the symmetric buffer's header, laid out from word 16.
     if stage_stamps and plan.stages > MAX_STAMPED_STAGES:
@@ -1066,7 +1151,15 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
             raise ValueError("trainkernel: the symmetric buffer's header has no room for this many ranks")
     emitter = _Emitter(plan)
     emitter.trace_stage = trace_stage
-    emitter.epilogue_lookahead = bool(epilogue_lookahead)
+    emitter.assume_aligned = bool(assume_aligned)
+    if wide_epilogue is None:
+        wide_epilogue = not plan.two_cta
+    if wide_epilogue and plan.uses_tc and not plan.background:
+        emitter.wide_epilogue = True
+        emitter.threads = THREADS + 32 * 4
+    if epilogue_lookahead not in (None, True, False, "first"):
+        raise ValueError('trainkernel: epilogue_lookahead must be True, False or "first"')
+    emitter.epilogue_lookahead = ("first" if emitter.wide_epilogue else True) if epilogue_lookahead is None else epilogue_lookahead
     if stream_piece not in (1, 2, 3, 6):
         raise ValueError("trainkernel: stream_piece must be 1, 2, 3 or 6")
     emitter.stream_piece = stream_piece
@@ -1092,6 +1185,10 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         dyn = 4 * (32 * 129 + 4 + 128 * 36) + 1024          # tk::SimtSmem + alignment slack
     if plan.uses_tc:
         dyn = 4 * (128 * 64 * 2 + 256 * 64 * 2) + 1024
+        if emitter.wide_epilogue:                            # one ring slot less: the room goes to four more transposition buffers
+            stages = (6 if plan.two_cta else {256: 4, 128: 6, 64: 8}[emitter.ring_bn]) - 1
+            dyn = max(stages * (128 * 64 * 2 + emitter.ring_bn * 64 * 2) + 1024,
+                      4 * (32 * 129 + 4 + 128 * 36) + 1024 if emitter.needs_simt else 0)
     return GeneratedKernel(
         source=source,
         workspace_elements=-(-plan.workspace_bytes // 4),
@@ -1105,6 +1202,9 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
         direct_state_commits=len(plan.direct_commits),
         threads=emitter.threads,
         dynamic_smem=dyn,
+        aligned_inputs=tuple(sorted(emitter.aligned_inputs)),
+        aligned_outputs=tuple(sorted(emitter.aligned_outputs)),
+        aligned_workspace=emitter.aligned_workspace,
         grid=plan.grid,
         tensor_maps=tuple(emitter.maps),
         input_count=len(plan.program.inputs) + extra_inputs,

@@ -20,7 +20,15 @@
 namespace tk {
 
 constexpr int kThreads = 192;          // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
-constexpr int kEpiThreads = 128;
+// Epilogue warps of the cta_group::1 GEMM: 4 (warps 2..5), or 8 in a kernel generated with the wide epilogue
+// (320 threads: warps 6..9 read the same TMEM quarters as warps 2..5 and take every other 32-column chunk; they
+// do nothing outside tensor-core GEMM units).  A generated kernel defines TK_EPI_WARPS before including this file.
+#ifndef TK_EPI_WARPS
+#define TK_EPI_WARPS 4
+#endif
+constexpr int kEpiWarps = TK_EPI_WARPS;
+static_assert(kEpiWarps == 4 || kEpiWarps == 8, "TK_EPI_WARPS must be 4 or 8");
+constexpr int kEpiThreads = 32 * kEpiWarps;
 constexpr int kWorkerWarps = kThreads / 32;   // warps that run a stage's units; work items are cut for kThreads threads
 // A kernel generated with stream warps is launched with kThreads + 32 * kStreamWarps threads: warps 6..9 do
 // nothing but the stage's memory-bound pieces (gradient exchange, FP32 updates) while warps 0..5 run its GEMMs.
@@ -36,8 +44,10 @@ constexpr int UMMA_K = 16;
 #endif
 constexpr int kRingBN = TK_RING_BN;
 static_assert(kRingBN == 64 || kRingBN == 128 || kRingBN == 256, "TK_RING_BN must be 64, 128 or 256");
-constexpr int kStages = kRingBN == 256 ? 4 : (kRingBN == 128 ? 6 : 8);   // cta_group::1 ring: 4 x 48, 6 x 32 or 8 x 24 KiB
-constexpr int kStages2 = 6;           // cta_group::2 ring: 6 x 32 KiB
+// cta_group::1 ring: 4 x 48, 6 x 32 or 8 x 24 KiB; one slot less where eight epilogue warps need the room for
+// their transposition buffers
+constexpr int kStages = (kRingBN == 256 ? 4 : (kRingBN == 128 ? 6 : 8)) - (kEpiWarps == 8 ? 1 : 0);
+constexpr int kStages2 = kEpiWarps == 8 ? 5 : 6;   // cta_group::2 ring: 6 x 32 KiB (5 with eight epilogue warps)
 constexpr int kMaxStages = 8;
 constexpr int kMaxBN = 256;            // accumulator pitch in TMEM columns
 constexpr int kSlotA = BM * BK * 2;    // 16 KiB
@@ -173,7 +183,7 @@ struct Dp {
 
 struct Ctx {
     Dp dp;
-    uint32_t* sync;        // {count, generation} of this launch's barrier slot
+    uint32_t* sync;        // this launch's barrier word (phase bit + arrival count)
     uint32_t* status;      // {code, stage, block, detail}
     uint64_t* stamps;      // timestamp area when the kernel was generated with stage stamps, else null
     uint32_t flags;        // launch flags (kTrustCarried)
@@ -259,16 +269,19 @@ __device__ __forceinline__ void ctx_finish(Ctx& c, bool use_tc) {
 }
 
 // ----------------------------------------------------------------------------
-// grid barrier: atomic arrive, generation spin, release/acquire at GPU scope.
-// The counter resets itself, so any number of launches and CUDA-graph replays
-// can reuse the same two words without host intervention.
+// grid barrier: ONE word, one atomic per block and barrier, release/acquire at GPU scope.
+// Bit 31 of the word is the barrier's phase, bits 0..30 count arrivals: block 0 adds
+// 2^31 - (arrivals - 1), every other block adds 1, so the arrivals of one barrier add up to exactly
+// 2^31: the phase bit flips when the last block arrives and the count is back at zero.  Nothing
+// is reset and nothing is read before arriving, so the word serves any number of barriers,
+// launches and CUDA-graph replays; a waiting block polls until the phase differs from the one its
+// own atomic returned, and the last arriver recognises itself by the count it was handed.
 // ----------------------------------------------------------------------------
 __device__ __forceinline__ void grid_barrier(Ctx& c) {
     fence_proxy_async();       // generic-proxy writes of this stage before later TMA reads
     __syncthreads();
     if (c.arrivals > 1 && threadIdx.x == 0 && !c.aborted()) {
-        uint32_t* count = c.sync;
-        uint32_t* gen = c.sync + 1;
+        uint32_t* word = c.sync;
         if (c.stamps != nullptr && c.stage_id < 64) {
             // barrier stall evidence: when block 0 arrived, and when the last block did (the timer only
             // grows, so the maximum left by earlier launches never wins)
@@ -276,19 +289,18 @@ __device__ __forceinline__ void grid_barrier(Ctx& c) {
             if (blockIdx.x == 0) c.stamps[kStampArrive + c.stage_id] = now;
             atomicMax(reinterpret_cast<unsigned long long*>(c.stamps + kStampLast + c.stage_id), static_cast<unsigned long long>(now));
         }
-        const uint32_t my_gen = ld_relaxed_gpu(gen);
-        const uint32_t arrived = atom_add_acq_rel_gpu(count, 1u);
-        if (arrived == c.arrivals - 1) {
-            st_relaxed_gpu(count, 0u);
-            st_release_gpu(gen, my_gen + 1u);
-        } else {
+        const bool leader = blockIdx.x == 0;
+        const uint32_t before = atom_add_acq_rel_gpu(word, leader ? 0x80000000u - (c.arrivals - 1u) : 1u);
+        const uint32_t counted = before & 0x7FFFFFFFu;
+        const bool last = leader ? counted == c.arrivals - 1u : counted == 0x7FFFFFFFu;
+        if (!last) {
             uint32_t polls = 0;
             uint64_t start = 0;
-            while (ld_acquire_gpu(gen) == my_gen) {
+            while (((ld_acquire_gpu(word) ^ before) & 0x80000000u) == 0u) {
                 if ((++polls & 0xFF) == 0) {
                     if (start == 0) start = global_timer_ns();
                     if (c.grid_aborted()) { *reinterpret_cast<volatile uint32_t*>(&c.sh->abort) = 1u; break; }
-                    if (global_timer_ns() - start > c.timeout_ns) { c.fail(kErrGridBarrier, arrived); break; }
+                    if (global_timer_ns() - start > c.timeout_ns) { c.fail(kErrGridBarrier, counted); break; }
                 }
             }
         }
@@ -509,6 +521,87 @@ __device__ __forceinline__ void st_row_stream(float* p, int nvalid, const float*
 }
 template <int W, typename T16>
 __device__ __forceinline__ void st_row_stream(T16* p, int nvalid, const float* v) { st_row<W>(p, nvalid, v); }
+
+// Row accesses of a tensor-core epilogue whose run of W elements is either wholly inside the tensor or wholly
+// outside it (nvalid is 0 or W) and, when inside, starts on a 16-byte boundary (8 bytes for four 16-bit
+// elements).  The code generator emits them where extents, strides and offsets prove both, and the host
+// refuses a launch whose base pointers would break the proof; what they save is the element-wise fallback
+// of ld_row / st_row, a third of an epilogue's instructions that never run but are fetched and stepped over
+// in code that executes once per launch.  STREAM selects the evict-first forms for FP32 data touched once.
+template <int W, bool STREAM>
+__device__ __forceinline__ void ld_row_full(const float* p, int nvalid, float* out) {
+    if constexpr (W % 4 == 0) {
+        if (nvalid != 0) {
+#pragma unroll
+            for (int j = 0; j < W; j += 4) {
+                const float4 v = STREAM ? ldg_stream(reinterpret_cast<const float4*>(p + j)) : *reinterpret_cast<const float4*>(p + j);
+                out[j] = v.x; out[j + 1] = v.y; out[j + 2] = v.z; out[j + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < W; ++j) out[j] = 0.0f;
+        }
+    } else {
+        ld_row<W>(p, nvalid, out);
+    }
+}
+template <int W, bool STREAM, typename T16>
+__device__ __forceinline__ void ld_row_full(const T16* p, int nvalid, float* out) {
+    static_assert(sizeof(T16) == 2, "16-bit element expected");
+    if constexpr (W % 4 == 0) {
+        if (nvalid != 0) {
+            constexpr int V = W % 8 == 0 ? 8 : 4;
+#pragma unroll
+            for (int j = 0; j < W; j += V) {
+                uint4 raw;
+                if constexpr (V == 8) raw = *reinterpret_cast<const uint4*>(p + j);
+                else { const uint2 half = *reinterpret_cast<const uint2*>(p + j); raw = make_uint4(half.x, half.y, 0u, 0u); }
+                const T16* h = reinterpret_cast<const T16*>(&raw);
+#pragma unroll
+                for (int e = 0; e < V; ++e) out[j + e] = to_f32(h[e]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < W; ++j) out[j] = 0.0f;
+        }
+    } else {
+        ld_row<W>(p, nvalid, out);
+    }
+}
+template <int W, bool STREAM>
+__device__ __forceinline__ void st_row_full(float* p, int nvalid, const float* v) {
+    if constexpr (W % 4 == 0) {
+        if (nvalid != 0) {
+#pragma unroll
+            for (int j = 0; j < W; j += 4) {
+                if constexpr (STREAM) stg_stream(reinterpret_cast<float4*>(p + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+                else *reinterpret_cast<float4*>(p + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+        }
+    } else {
+        st_row<W>(p, nvalid, v);
+    }
+}
+template <int W, bool STREAM, typename T16>
+__device__ __forceinline__ void st_row_full(T16* p, int nvalid, const float* v) {
+    static_assert(sizeof(T16) == 2, "16-bit element expected");
+    if constexpr (W % 4 == 0) {
+        if (nvalid != 0) {
+            constexpr int V = W % 8 == 0 ? 8 : 4;
+#pragma unroll
+            for (int j = 0; j < W; j += V) {
+                uint4 raw;
+                T16* h = reinterpret_cast<T16*>(&raw);
+#pragma unroll
+                for (int e = 0; e < V; ++e) from_f32(h + e, v[j + e]);
+                if constexpr (V == 8) *reinterpret_cast<uint4*>(p + j) = raw;
+                else *reinterpret_cast<uint2*>(p + j) = make_uint2(raw.x, raw.y);
+            }
+        }
+    } else {
+        st_row<W>(p, nvalid, v);
+    }
+}
 
 // Barrier among the kThreads worker threads (warps 0..5) only: stream warps, where a kernel has them, are
 // busy elsewhere and must not be waited for.  In a kernel of kThreads threads it is a block barrier.
@@ -907,36 +1000,48 @@ __device__ __forceinline__ void epilogue_chunk(Ctx& c, const Params& P, const fl
     __syncwarp();
 }
 
-// The epilogue of one accumulator tile of TN columns starting at tile column `tile_col0`: 32-column chunks, two per
-// iteration so that the operand buffers alternate without run-time indexing.  With Epi::kPipelined the operands
-// of chunk i + 1 are requested before chunk i is read out of TMEM; `first` must then already hold chunk 0's.
+// The epilogue of one accumulator tile of TN columns starting at tile column `tile_col0`, as seen by one warp:
+// the 32-column chunks `chunk0`, `chunk0 + step`, ... (step 1: the warp has its TMEM quarter to itself; step 2:
+// two warps share the quarter and take alternate chunks).  With Epi::kPipelined the operands of the warp's
+// next chunk are requested before the current one is read out of TMEM (two chunks per iteration, so that the
+// two operand buffers alternate without run-time indexing); `first` must then already hold those of chunk
+// `chunk0`, as it must with Epi::kFetchFirst (the caller requested them before it waited for the
+// accumulator; later chunks fetch their own at their start).
 template <int TN, typename Epi, typename Params>
 __device__ __forceinline__ void epilogue_tile(Ctx& c, const Params& P, uint32_t taddr, int row0, int tile_col0, int N,
-                                              typename EpiOps<Epi>::type& first) {
+                                              typename EpiOps<Epi>::type& first, int chunk0 = 0, int step = 1) {
+    const int stride = 32 * step;                          // columns between this warp's consecutive chunks
+    if constexpr (!Epi::kPipelined) {
+        // one chunk body, executed once per chunk: half the code of the look-ahead form below, which matters in
+        // kernels whose every GEMM runs its epilogue a handful of times per launch (instruction fetch is cold)
+#pragma unroll 1
+        for (int cc = 32 * chunk0; cc < TN; cc += stride) {
+            const int col0 = tile_col0 + cc;
+            if (col0 >= N) break;                          // warp-uniform
+            if (!(Epi::kFetchFirst && cc == 32 * chunk0)) epilogue_fetch<Epi>(c, P, row0, col0, min(32, N - col0), first);
+            float acc[32];
+            tc_ld32(taddr + cc, acc);
+            tc_wait_ld();
+            epilogue_chunk<Epi>(c, P, acc, row0, col0, min(32, N - col0), first);
+        }
+        return;
+    }
     typename EpiOps<Epi>::type second;
 #pragma unroll 1
-    for (int cc = 0; cc < TN; cc += 64) {
+    for (int cc = 32 * chunk0; cc < TN; cc += 2 * stride) {
         const int col0 = tile_col0 + cc;
         if (col0 >= N) break;                              // warp-uniform
-        const bool pair = col0 + 32 < N;
-        if constexpr (Epi::kPipelined) {
-            if (pair) epilogue_fetch<Epi>(c, P, row0, col0 + 32, min(32, N - col0 - 32), second);
-        } else {
-            epilogue_fetch<Epi>(c, P, row0, col0, min(32, N - col0), first);
-        }
+        const bool pair = cc + stride < TN && col0 + stride < N;
+        if (pair) epilogue_fetch<Epi>(c, P, row0, col0 + stride, min(32, N - col0 - stride), second);
         float acc[32];
         tc_ld32(taddr + cc, acc);
         tc_wait_ld();
         epilogue_chunk<Epi>(c, P, acc, row0, col0, min(32, N - col0), first);
         if (!pair) break;
-        if constexpr (Epi::kPipelined) {
-            if (cc + 64 < TN && col0 + 64 < N) epilogue_fetch<Epi>(c, P, row0, col0 + 64, min(32, N - col0 - 64), first);
-        } else {
-            epilogue_fetch<Epi>(c, P, row0, col0 + 32, min(32, N - col0 - 32), second);
-        }
-        tc_ld32(taddr + cc + 32, acc);
+        if (cc + 2 * stride < TN && col0 + 2 * stride < N) epilogue_fetch<Epi>(c, P, row0, col0 + 2 * stride, min(32, N - col0 - 2 * stride), first);
+        tc_ld32(taddr + cc + stride, acc);
         tc_wait_ld();
-        epilogue_chunk<Epi>(c, P, acc, row0, col0 + 32, min(32, N - col0 - 32), second);
+        epilogue_chunk<Epi>(c, P, acc, row0, col0 + stride, min(32, N - col0 - stride), second);
     }
 }
 
@@ -1028,29 +1133,33 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
             }
         }
         __syncwarp();
-    } else if (c.warp < kWorkerWarps) {
+    } else if (c.warp < 2 + kEpiWarps) {
         const int quarter = c.warp & 3;                // TMEM lanes this warp may read
+        const int chunk0 = (c.warp - 2) >> 2;          // wide epilogue: warps 6..9 start one chunk later ...
+        constexpr int kChunkStep = kEpiWarps / 4;      // ... and every warp takes every other chunk
         for (int64_t t = first_item(item_base); t < tiles && !c.aborted(); t += step) {
             int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
-            if (t == first_item(item_base)) {
+            if (chunk0 == 0 && t == first_item(item_base)) {
                 // the block's first tile of this unit: nobody fetched its epilogue operands yet, and these warps
                 // are idle until the accumulator is complete
                 const int prow = tm * BM + quarter * 32 + c.lane;
                 if (prow < M) Epi::prefetch(P, prow, tn * BN, min(BN, N - tn * BN));
             }
-            if (t + step < tiles) {
+            if (chunk0 == 0 && t + step < tiles) {
                 int pm, pn; tile_coords(t + step, tiles_m, tiles_n, pm, pn);
                 const int prow = pm * BM + quarter * 32 + c.lane;
                 if (prow < M && pn * BN < N) Epi::prefetch(P, prow, pn * BN, min(BN, N - pn * BN));
             }
             const int row0 = tm * BM + quarter * 32;
             typename EpiOps<Epi>::type operands;
-            if constexpr (Epi::kPipelined) epilogue_fetch<Epi>(c, P, row0, tn * BN, min(32, N - tn * BN), operands);   // in flight during the wait
+            if constexpr (Epi::kPipelined || Epi::kFetchFirst) {               // in flight during the wait
+                if (tn * BN + 32 * chunk0 < N) epilogue_fetch<Epi>(c, P, row0, tn * BN + 32 * chunk0, min(32, N - tn * BN - 32 * chunk0), operands);
+            }
             if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
             tc_fence_after();
             if (threadIdx.x == 64) TK_TRACE(4, t);
             const uint32_t taddr = c.tmem + c.acc * kMaxBN + (static_cast<uint32_t>(quarter * 32) << 16);
-            epilogue_tile<BN, Epi>(c, P, taddr, row0, tn * BN, N, operands);
+            epilogue_tile<BN, Epi>(c, P, taddr, row0, tn * BN, N, operands, chunk0, kChunkStep);
             tc_fence_before();
             __syncwarp();
             if (c.lane == 0) mbar_arrive(&sh->tmem_empty[c.acc]);

@@ -170,22 +170,26 @@ __device__ __forceinline__ void gemm_tc2(Ctx& c, const Params& P, const CUtensor
             }
         }
         __syncwarp();
-    } else if (c.warp < kWorkerWarps) {
+    } else if (c.warp < 2 + kEpiWarps) {
         const int quarter = c.warp & 3;
+        const int chunk0 = (c.warp - 2) >> 2;          // wide epilogue: warps 6..9 start one chunk later ...
+        constexpr int kChunkStep = kEpiWarps / 4;      // ... and every warp takes every other chunk
         for (int64_t t = first; t < tiles && !c.aborted(); t += clusters) {
             int tm, tn; pair_coords<GROUP>(t, tiles_m, tiles_n, tm, tn);
-            if (t + clusters < tiles) {
+            if (chunk0 == 0 && t + clusters < tiles) {
                 int pm, pn; pair_coords<GROUP>(t + clusters, tiles_m, tiles_n, pm, pn);
                 const int prow = pm * TM + static_cast<int>(rank) * 128 + quarter * 32 + c.lane;
                 if (prow < M && pn * TN < N) Epi::prefetch(P, prow, pn * TN, min(TN, N - pn * TN));
             }
             const int row0 = tm * TM + static_cast<int>(rank) * 128 + quarter * 32;
             typename EpiOps<Epi>::type operands;
-            if constexpr (Epi::kPipelined) epilogue_fetch<Epi>(c, P, row0, tn * TN, min(32, N - tn * TN), operands);   // in flight during the wait
+            if constexpr (Epi::kPipelined || Epi::kFetchFirst) {               // in flight during the wait
+                if (tn * TN + 32 * chunk0 < N) epilogue_fetch<Epi>(c, P, row0, tn * TN + 32 * chunk0, min(32, N - tn * TN - 32 * chunk0), operands);
+            }
             if (!c.wait(&sh->tmem_full[c.acc], c.acc_phase, kErrTmemFull)) break;
             tc_fence_after();
             const uint32_t taddr = c.tmem + c.acc * kMaxBN + (static_cast<uint32_t>(quarter * 32) << 16);
-            epilogue_tile<TN, Epi>(c, P, taddr, row0, tn * TN, N, operands);
+            epilogue_tile<TN, Epi>(c, P, taddr, row0, tn * TN, N, operands, chunk0, kChunkStep);
             tc_fence_before();
             __syncwarp();
             if (c.lane == 0) {

@@ -82,7 +82,7 @@ int check(CUresult result, const char* what) {
     return fail(static_cast<int>(result), "trainkernel: %s failed: %s", what, text ? text : "unknown CUDA error");
 }
 
-constexpr int kSyncSlots = 64;        // one {count, generation} pair per 128-byte line
+constexpr int kSyncSlots = 64;        // one barrier word (phase bit + arrival count) per 128-byte line
 constexpr int kSyncStride = 128;
 constexpr int kStampCount = 256;     // stage stamps | block 0's barrier arrivals | latest arrivals | peer waits + role trace
 constexpr int kMapWays = 4;           // encoded tensor maps remembered per map slot
@@ -131,6 +131,10 @@ struct tk_module {
     std::atomic<size_t> workspace_bytes{0};  // what the kernel's plan needs (0: not recorded)
     std::atomic<uint64_t> launches{0};       // launches issued through this module
     std::atomic<int> faulted{0};      // tk_module_status saw an error; launches are refused until tk_module_reset
+    // Base pointers the kernel's vector accesses take to be 16-byte aligned (bit i: input / output i; set once,
+    // right after the module is created, before any launch).
+    std::vector<uint8_t> aligned_in, aligned_out;
+    std::atomic<int> aligned_workspace{0};
     std::atomic<unsigned long long> capture_id{0};   // last stream capture a launch was recorded into
 
     CUdeviceptr sync_slot(uint32_t i) const { return state + static_cast<size_t>(i) * kSyncStride; }
@@ -220,6 +224,15 @@ int tk_module_launch_flags(tk_module* m, const void* const* inputs, void* const*
     if (grid > m->max_blocks || grid % m->cluster)
         return fail(TK_E_CAPACITY, "trainkernel: grid %d exceeds the %d co-resident blocks a cooperative launch allows (cluster size %d)", grid,
                     m->max_blocks, m->cluster);
+    // Pointers the kernel reads and writes with 16-byte vector accesses: a misaligned one would fault on the device.
+    for (size_t i = 0; i < m->aligned_in.size() && i < static_cast<size_t>(m->n_inputs); ++i)
+        if (m->aligned_in[i] && (reinterpret_cast<uintptr_t>(inputs[i]) & 15))
+            return fail(TK_E_ARGUMENT, "trainkernel: input %zu is not 16-byte aligned (this kernel was generated for aligned tensors; generate it with assume_aligned=False)", i);
+    for (size_t i = 0; i < m->aligned_out.size() && i < static_cast<size_t>(m->n_outputs); ++i)
+        if (m->aligned_out[i] && (reinterpret_cast<uintptr_t>(outputs[i]) & 15))
+            return fail(TK_E_ARGUMENT, "trainkernel: output %zu is not 16-byte aligned (this kernel was generated for aligned tensors; generate it with assume_aligned=False)", i);
+    if (m->aligned_workspace.load() && (reinterpret_cast<uintptr_t>(workspace) & 15))
+        return fail(TK_E_ARGUMENT, "trainkernel: the workspace is not 16-byte aligned");
     // Kernel parameter block: tensor maps, input pointers, output pointers, then the scalars.
     alignas(64) unsigned char block[8192];
     if (m->param_bytes > sizeof(block)) return fail(TK_E_ARGUMENT, "trainkernel: parameter block too large");
@@ -416,6 +429,15 @@ int tk_module_device(tk_module* m, int* out) {
 int tk_module_launches(tk_module* m, uint64_t* out) {
     if (!m || !out) return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_launches");
     *out = m->launches.load();
+    return 0;
+}
+
+int tk_module_require_alignment(tk_module* m, const uint8_t* inputs, int n_inputs, const uint8_t* outputs, int n_outputs, int workspace) {
+    if (!m || n_inputs < 0 || n_outputs < 0 || n_inputs > m->n_inputs || n_outputs > m->n_outputs || (n_inputs && !inputs) || (n_outputs && !outputs))
+        return fail(TK_E_ARGUMENT, "trainkernel: invalid argument to tk_module_require_alignment");
+    m->aligned_in.assign(inputs, inputs + n_inputs);
+    m->aligned_out.assign(outputs, outputs + n_outputs);
+    m->aligned_workspace.store(workspace ? 1 : 0);
     return 0;
 }
 

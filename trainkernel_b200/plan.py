@@ -216,8 +216,9 @@ class Planner:
                  fuse_pointwise: bool = True, fuse_epilogues: bool = True, max_blocks: int | None = None,
                  tensor_cores: bool = True, block_n: int | None = None, two_cta: bool | None = None, world: int = 1, background: bool = False,
                  multicast: bool = False, cluster_barrier: bool | None = None, carry: bool | str | None = None,
-                 wave_aware_tiles: bool = False, exchange_chunks: int = EXCHANGE_CHUNKS_PER_ITEM):
+                 wave_aware_tiles: bool = False, exchange_chunks: int = EXCHANGE_CHUNKS_PER_ITEM, late_casts: bool = False):
         self.program = program
+        self.late_casts = bool(late_casts)
         if exchange_chunks not in (8, 16):
             raise ValueError("trainkernel: exchange_chunks must be 8 or 16")
         self.exchange_chunks = exchange_chunks
@@ -820,7 +821,7 @@ class Planner:
         # Streams that depend on nothing but program inputs (the BF16 weight shadows) run as late as
         # their first consumer allows, in a stage that has tensor-core GEMMs, where the epilogue warps
         # execute them in the background instead of in a stage of their own.
-        tensor_stages = {u.stage for u in units if u.kind == "gemm" and u.path == "tc"} if self.background else set()
+        tensor_stages = {u.stage for u in units if u.kind == "gemm" and u.path == "tc"} if self.background or self.late_casts else set()
         for unit in units:
             if unit.kind != "point" or any(buffer in writer for buffer in unit.reads):
                 continue

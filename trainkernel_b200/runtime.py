@@ -95,6 +95,7 @@ def library() -> ctypes.CDLL:
         lib.tk_module_device.argtypes = [p, ctypes.POINTER(i32)]
         lib.tk_module_launches.argtypes = [p, ctypes.POINTER(u64)]
         lib.tk_module_set_workspace_bytes.argtypes = [p, ctypes.c_size_t]
+        lib.tk_module_require_alignment.argtypes = [p, ctypes.c_char_p, i32, ctypes.c_char_p, i32, i32]
         lib.tk_module_workspace_bytes.argtypes = [p, ctypes.POINTER(ctypes.c_size_t)]
         lib.tk_module_resource_usage.argtypes = [p, ctypes.POINTER(ctypes.c_int64)]
         lib.tk_module_max_coresident_blocks.argtypes = [p, ctypes.POINTER(i32)]
@@ -186,6 +187,12 @@ class _Module:
         self.handle = handle
         self.lib = lib
         lib.tk_module_set_workspace_bytes(handle, generated.workspace_bytes)
+        if generated.aligned_inputs or generated.aligned_outputs or generated.aligned_workspace:
+            wanted_in = bytes(int(i in generated.aligned_inputs) for i in range(generated.input_count))
+            wanted_out = bytes(int(i in generated.aligned_outputs) for i in range(generated.output_count))
+            code = lib.tk_module_require_alignment(handle, wanted_in, len(wanted_in), wanted_out, len(wanted_out), int(generated.aligned_workspace))
+            if code:
+                _raise(code)
         if generated.cluster > 1:
             code = lib.tk_module_set_cluster(handle, generated.cluster)
             if code:
@@ -469,6 +476,8 @@ def compile_program(program: Program, example_inputs: tuple[Any, ...] | list[Any
     capability = torch.cuda.get_device_capability(device)
     if capability[0] != 10:
         raise RuntimeError(f"trainkernel: an sm_100 (B200-class) GPU is required, found compute capability {capability[0]}.{capability[1]}")
+    if "assume_aligned" not in options and any(x.data_ptr() % 16 for x in flat):
+        options["assume_aligned"] = False     # example tensors at odd offsets: keep the element-wise fallbacks
     generated = generate(program, inplace_outputs=inplace_outputs, **options)
     if any(flat[i].requires_grad for i in (inplace_outputs or {}).values()):
         raise ValueError("trainkernel: inplace targets must be detached from autograd")
