@@ -77,6 +77,11 @@ def test_stage_profile_is_consistent_with_event_timing(name):
             assert "barrier_wait_us" in profiled and profiled["barrier_release_us"] < 100.0
     else:
         assert stalls == []           # one-cluster kernels synchronise in hardware: nothing to stamp
+    # prologue, stages and tail add up to the launch as the device saw it, inside the event interval
+    span = compiled.runner.launch_span()
+    assert span["prologue"] >= 0 and span["tail"] >= 0 and span["stages"] == stamps[-1] - stamps[0]
+    assert span["total"] == span["prologue"] + span["stages"] + span["tail"]
+    assert span["total"] / 1e6 <= begin.elapsed_time(end) + 0.005
 
 
 # ---------------------------------------------------------------------------------------------

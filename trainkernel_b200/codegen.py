@@ -946,6 +946,8 @@ class _Emitter:
         ]
         if plan.uses_tc:
             entry.append("    __shared__ tk::EpiStage epi_stage;")
+        if stage_stamps:
+            entry.append("    const uint64_t tk_entered = tk::global_timer_ns();   // before the prologue (barrier set-up, tensor memory, map prefetch)")
         entry += [
             "    tk::Ctx c;",
             "    tk::ctx_init2(c, P.sync, P.status, P.timeout_ns, P.arrivals, &shared_state, dyn_smem);" if plan.two_cta else
@@ -972,7 +974,7 @@ class _Emitter:
             entry.append("    if (threadIdx.x == 0) tk_carry_phase = P.status[tk::kCarryPhaseWord] & 1u;")
             entry.append("    __syncthreads();")
         if stage_stamps:
-            entry.append("    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[0] = tk::global_timer_ns();")
+            entry.append("    if (blockIdx.x == 0 && threadIdx.x == 0) { P.stamps[0] = tk::global_timer_ns(); P.stamps[tk::kStampTrace + 6] = tk_entered; }")
         tail = []
         if plan.carry_bytes:
             tail.append("    if (blockIdx.x == 0 && threadIdx.x == 0) P.status[tk::kCarriedWord] = (c.aborted() || c.grid_aborted()) ? 0u : 1u;")
@@ -980,7 +982,11 @@ class _Emitter:
             tail.append(f"    __syncthreads();\n    if (blockIdx.x == 0 && threadIdx.x == 0) P.stamps[{plan.stages}] = tk::global_timer_ns();")
         if exchanging:
             tail.append("    if (blockIdx.x == 0 && threadIdx.x == 0) tk::dp_finish(c.dp);")
-        tail += ["    tk::ctx_finish2(c);" if plan.two_cta else f"    tk::ctx_finish(c, {use_tc});", "}", ""]
+        tail += ["    tk::ctx_finish2(c);" if plan.two_cta else f"    tk::ctx_finish(c, {use_tc});"]
+        if stage_stamps:
+            # when the last block is done with its epilogue (tensor memory released): the end of the launch as the device sees it
+            tail.append("    if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned long long*>(P.stamps + tk::kStampTrace + 7), static_cast<unsigned long long>(tk::global_timer_ns()));")
+        tail += ["}", ""]
         return "\n".join(header + self.functors + entry + [body.text()] + tail)
 
 

@@ -358,6 +358,15 @@ class CompiledProgram:
                             "release": release - last, "peer_wait": words[192 + barrier + 1] if self.generated.world > 1 else 0})
         return records
 
+    def launch_span(self) -> dict:
+        """Where the last launch spent its time outside the stages (kernel generated with `stage_stamps=True`),
+        nanoseconds: `prologue` from block 0's first instruction to the start of stage 0 (barrier set-up, tensor
+        memory allocation, tensor-map prefetch), `stages` from there to block 0's end of the last stage, `tail`
+        from there until the last block has released its tensor memory, `total` first instruction to that point."""
+        words = self._stamps(256)
+        entered, first, last, left = words[254], words[0], words[self.generated.stages], words[255]
+        return {"prologue": first - entered, "stages": last - first, "tail": left - last, "total": left - entered}
+
     def role_trace(self) -> list[int]:
         """The six role-level %globaltimer values of the traced tile (kernel generated with `trace_stage=`)."""
         return self._stamps(256)[248:254]
