@@ -358,3 +358,17 @@ def test_single_cta_tensor_core_kernels_get_eight_epilogue_warps():
     assert asked.threads == 320 and asked.dynamic_smem == 5 * 32768 + 1024
     plain, plain_inplace = _step_program("c1")
     assert generate(plain, inplace_outputs=plain_inplace).threads == 192
+
+
+def test_simt_gemms_stage_no_deeper_than_their_k():
+    work = workloads.mlp_workload("tiny_online", (32, 64, 16), 4)
+    program, _ = tk.capture(work.fn(), (work.state, *work.batches[0]))
+    g = generate(program, inplace_outputs={5 + i: i for i in range(4)})
+    import re
+    depths = {name: int(depth) for depth, name in re.findall(r"tk::gemm_simt<(\d+), [^>]*?Epi_(\w+)>", g.source)}
+    assert depths and set(depths.values()) <= {32, 64}                 # K is 32, 64, 16, 4 and 4 in this program
+    assert depths["mm"] == 32 and depths["mm_1"] == 64
+    forced = generate(program, inplace_outputs={5 + i: i for i in range(4)}, simt_depth=128)
+    assert set(re.findall(r"tk::gemm_simt<(\d+),", forced.source)) == {"128"}
+    with pytest.raises(ValueError, match="simt_depth"):
+        generate(program, simt_depth=48)

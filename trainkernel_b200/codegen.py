@@ -132,6 +132,7 @@ class _Emitter:
         self.rows = False
         self.background = plan.background
         self.wide_epilogue = False       # eight epilogue warps per cta_group::1 GEMM tile instead of four
+        self.simt_depth = None           # K depth a SIMT GEMM stages per step; None: 32, 64 or 128 by the product's K
         self.assume_aligned = True       # tensor-core epilogues may lean on 16-byte aligned base pointers (checked at launch)
         self._full_rows = False          # set while the functor of such an epilogue is written
         self.aligned_inputs: set[int] = set()
@@ -534,7 +535,8 @@ class _Emitter:
                       f"{self.pointer(b.buffer, b.dtype, True)} + {b.offset}LL, {ld}LL, {n}, {k}, {base}LL);")
         else:
             self.needs_simt = True
-            body.emit(f"tk::gemm_simt<{CTYPE[a.dtype]}, {ROUND[a.round_to]}, {CTYPE[b.dtype]}, {ROUND[b.round_to]}, {epi}>(c, P, reinterpret_cast<tk::SimtSmem*>(c.slots), "
+            depth = self.simt_depth or (32 if k <= 32 else 64 if k <= 64 else 128)
+            body.emit(f"tk::gemm_simt<{depth}, {CTYPE[a.dtype]}, {ROUND[a.round_to]}, {CTYPE[b.dtype]}, {ROUND[b.round_to]}, {epi}>(c, P, reinterpret_cast<tk::SimtSmem*>(c.slots), "
                       f"{self.pointer(a.buffer, a.dtype, True)} + {a.offset}LL, {a.strides[0]}LL, {a.strides[1]}LL, "
                       f"{self.pointer(b.buffer, b.dtype, True)} + {b.offset}LL, {b.strides[0]}LL, {b.strides[1]}LL, {m}, {n}, {k}, {base}LL);")
 
@@ -1062,7 +1064,7 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
              carry_shadows: bool | str | None = None, epilogue_lookahead: bool | None = None, stream_piece: int = 3,
              stream_everything: bool = False, wave_aware_tiles: bool = False, exchange_chunks: int = 8,
              wide_epilogue: bool | None = None, late_casts: bool = False, assume_aligned: bool = True,
-             **reference_knobs) -> GeneratedKernel:
+             simt_depth: int | None = None, **reference_knobs) -> GeneratedKernel:
     """Generate the sm_100a kernel source and launch metadata for `program`.
 
     The reference's SM80/SM90 geometry knobs (`blocks_per_sm`, `gemm_k_tile`,
@@ -1117,6 +1119,10 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     epilogue's instructions; small programs, which fetch every stage's code cold in every launch, run
     2-11 % faster without it.
 
+    `simt_depth`: K depth a SIMT GEMM stages in shared memory per step (default: 32, 64 or 128 by the
+    product's K; the loads of a step are unrolled per staged position, so a shallow product should not carry
+    the code of a deep one).
+
     `late_casts`: place a cast of a program input (a BF16 weight copy) in the stage before its first reader
     instead of the first stage when that stage has tensor-core GEMMs (no measurable difference; off).
 
@@ -1158,6 +1164,9 @@ def generate(program: Program, *, fuse_pointwise: bool = True, fuse_epilogues: b
     emitter = _Emitter(plan)
     emitter.trace_stage = trace_stage
     emitter.assume_aligned = bool(assume_aligned)
+    if simt_depth not in (None, 32, 64, 128):
+        raise ValueError("trainkernel: simt_depth must be 32, 64 or 128")
+    emitter.simt_depth = simt_depth
     if wide_epilogue is None:
         wide_epilogue = not plan.two_cta
     if wide_epilogue and plan.uses_tc and not plan.background:

@@ -1179,9 +1179,12 @@ __device__ __forceinline__ void gemm_tc(Ctx& c, const Params& P, const CUtensorM
 constexpr int kSimtK = 128;            // K depth staged per step: few steps, many loads in flight per step
 struct alignas(16) SimtSmem { float a[32][kSimtK + 1]; float pad[4 - (32 * (kSimtK + 1)) % 4]; float b[kSimtK][36]; };
 
-template <typename TA, typename RA, typename TB, typename RB, typename Epi, typename Params>
+template <int KS, typename TA, typename RA, typename TB, typename RB, typename Epi, typename Params>
 __device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm, const TA* A, int64_t a_rs, int64_t a_ks,
                                           const TB* B, int64_t b_ks, int64_t b_cs, int M, int N, int K, int64_t item_base) {
+    // KS: the K depth staged per step (32, 64 or 128 = kSimtK, the buffers' size).  The loads of a step are
+    // unrolled per staged position, so a product whose K is 32 should not carry the code of 128.
+    static_assert(KS == 32 || KS == 64 || KS == kSimtK, "staging depth");
     const int tiles_n = (N + 31) / 32;
     const int64_t tiles = static_cast<int64_t>((M + 31) / 32) * tiles_n;
     const int tid = threadIdx.x;
@@ -1190,22 +1193,22 @@ __device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm,
     for (int64_t t = first_item(item_base); t < tiles; t += gridDim.x) {
         const int row0 = static_cast<int>(t / tiles_n) * 32, col0 = static_cast<int>(t % tiles_n) * 32;
         float acc[2][4] = {};
-        for (int k0 = 0; k0 < K; k0 += kSimtK) {
-            const int depth = min(kSimtK, K - k0);
+        for (int k0 = 0; k0 < K; k0 += KS) {
+            const int depth = min(KS, K - k0);
             worker_sync();
             // Stage A[32, depth] and B[depth, 32].  Positions are decomposed against the fixed staging
             // depth (shifts and masks, no division by a runtime value) and the part beyond `depth` is
             // skipped.  A thread issues ALL of its loads of the step (22 per operand) before its first
             // shared-memory store: one round trip to memory per step.  Consecutive threads walk the
             // unit-stride axis of each operand.
-            constexpr int kPerThread = (32 * kSimtK + kThreads - 1) / kThreads;
+            constexpr int kPerThread = (32 * KS + kThreads - 1) / kThreads;
             float va[kPerThread], vb[kPerThread];
 #pragma unroll
             for (int u = 0; u < kPerThread; ++u) {
                 const int p = tid + u * kThreads;
-                const int ar = a_k_fast ? p / kSimtK : p % 32, ak = a_k_fast ? p % kSimtK : p / 32;
-                const int bk = b_n_fast ? p / 32 : p % kSimtK, bc = b_n_fast ? p % 32 : p / kSimtK;
-                const bool in_tile = p < 32 * kSimtK;
+                const int ar = a_k_fast ? p / KS : p % 32, ak = a_k_fast ? p % KS : p / 32;
+                const int bk = b_n_fast ? p / 32 : p % KS, bc = b_n_fast ? p % 32 : p / KS;
+                const bool in_tile = p < 32 * KS;
                 const int gr = row0 + ar, gc = col0 + bc;
                 va[u] = (in_tile && ak < depth && gr < M) ? RA::rnd(to_f32(A[static_cast<int64_t>(gr) * a_rs + static_cast<int64_t>(k0 + ak) * a_ks])) : 0.0f;
                 vb[u] = (in_tile && bk < depth && gc < N) ? RB::rnd(to_f32(B[static_cast<int64_t>(k0 + bk) * b_ks + static_cast<int64_t>(gc) * b_cs])) : 0.0f;
@@ -1213,9 +1216,9 @@ __device__ __forceinline__ void gemm_simt(Ctx& c, const Params& P, SimtSmem* sm,
 #pragma unroll
             for (int u = 0; u < kPerThread; ++u) {
                 const int p = tid + u * kThreads;
-                const int ar = a_k_fast ? p / kSimtK : p % 32, ak = a_k_fast ? p % kSimtK : p / 32;
-                const int bk = b_n_fast ? p / 32 : p % kSimtK, bc = b_n_fast ? p % 32 : p / kSimtK;
-                if (p < 32 * kSimtK) {
+                const int ar = a_k_fast ? p / KS : p % 32, ak = a_k_fast ? p % KS : p / 32;
+                const int bk = b_n_fast ? p / 32 : p % KS, bc = b_n_fast ? p % 32 : p / KS;
+                if (p < 32 * KS) {
                     if (ak < depth) sm->a[ar][ak] = va[u];
                     if (bk < depth) sm->b[bk][bc] = vb[u];
                 }
