@@ -128,8 +128,12 @@ def test_path_selection():
         program, _ = tk.capture(fn, tensors)
         return [u[3] for u in generate(program, **options).units if u[1] == "gemm"]
     bf = torch.bfloat16
-    assert paths(lambda a, b: a @ b, torch.randn(64, 64).to(bf), torch.randn(64, 64).to(bf)) == ["tc"]
-    assert paths(lambda a, b: a @ b, torch.randn(64, 64).to(bf), torch.randn(64, 64).to(bf), tensor_cores=False) == ["simt"]
+    assert paths(lambda a, b: a @ b, torch.randn(128, 64).to(bf), torch.randn(64, 64).to(bf)) == ["tc"]
+    assert paths(lambda a, b: a @ b, torch.randn(128, 64).to(bf), torch.randn(64, 64).to(bf), tensor_cores=False) == ["simt"]
+    # a program whose largest product is below 0.6 MFLOP stays off the tensor path altogether ...
+    assert paths(lambda a, b: a @ b, torch.randn(64, 64).to(bf), torch.randn(64, 64).to(bf)) == ["simt"]
+    # ... but one large product keeps the small ones of the same program on it
+    assert paths(lambda a, b, c: (a @ b) @ c, torch.randn(128, 64).to(bf), torch.randn(64, 64).to(bf), torch.randn(64, 16).to(bf)) == ["tc", "tc"]
     assert paths(lambda a, b: a @ b, torch.randn(64, 64), torch.randn(64, 64)) == ["simt"]
     assert paths(lambda a, b: a @ b, torch.randn(17, 33).to(bf), torch.randn(33, 65).to(bf)) == ["simt"]   # 66-byte rows
     assert paths(lambda a, b: a @ b, torch.randn(1, 128).to(bf), torch.randn(128, 64).to(bf)) == ["gemv"]

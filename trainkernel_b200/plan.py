@@ -38,6 +38,7 @@ ALIGN = 256
 # flight through the switch.  16 was tried (`exchange_chunks=16`): the item then needs more registers than a
 # called function gets without saving its caller's, and the step was no faster (4 ranks, p50 of 30 replays:
 # 2.81 ms against 2.75 ms with 8).
+TENSOR_CORE_MIN_FLOPS = 600_000   # 2*M*N*K of the largest product below which a program stays off the tensor path (MLP 32-64-16, batch 16: 17.9 -> 12.0 us per step; the tiny MLP of the benchmark, 1.05 MFLOP per product, is the same either way)
 EXCHANGE_CHUNKS_PER_ITEM = 8
 
 
@@ -238,6 +239,11 @@ class Planner:
         self.background = background
         self.multicast = bool(multicast) and world > 1
         self.ops = list(program.operations)
+        # A program whose largest product is below TENSOR_CORE_MIN_FLOPS runs all of them on the SIMT path: the
+        # tensor path's fixed costs (tensor-memory allocation, tensor maps, the latency of a TMA round trip and
+        # of an accumulator hand-over per tile) are then larger than the products themselves.
+        products = [op for op in self.ops if op.op in ("mm", "addmm")]
+        self.tiny_products = bool(products) and all(2 * prod(op.output.shape) * (op.inputs[-2].shape[1] if isinstance(op.inputs[-2], TensorSpec) and len(op.inputs[-2].shape) == 2 else 1 << 30) < TENSOR_CORE_MIN_FLOPS for op in products)
         self.index = {op.output.buffer: i for i, op in enumerate(self.ops)}
         self.producer = {op.output.buffer: op for op in self.ops}
         self.input_index = {spec.buffer: i for i, spec in enumerate(program.inputs)}
@@ -460,7 +466,7 @@ class Planner:
         sixteen = a_spec.dtype == b_spec.dtype and a_spec.dtype in ("bfloat16", "float16")
         a_major = self._tma_major(m, k, a_spec.strides, a_spec.offset)
         b_major = self._tma_major(n, k, (b_spec.strides[1], b_spec.strides[0]), b_spec.offset)
-        want_tc = bool(self.tensor_cores and sixteen and m > 4 and k > 8 and n >= 8 and a_major and b_major)
+        want_tc = bool(self.tensor_cores and not self.tiny_products and sixteen and m > 4 and k > 8 and n >= 8 and a_major and b_major)
         unit.a = self._gemm_operand(a_spec, want_tc)
         unit.b = self._gemm_operand(b_spec, want_tc)
         if want_tc:
