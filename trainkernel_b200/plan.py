@@ -242,8 +242,14 @@ class Planner:
         # A program whose largest product is below TENSOR_CORE_MIN_FLOPS runs all of them on the SIMT path: the
         # tensor path's fixed costs (tensor-memory allocation, tensor maps, the latency of a TMA round trip and
         # of an accumulator hand-over per tile) are then larger than the products themselves.
+        def product_flops(op: Operation) -> int:
+            left = op.inputs[-2]                     # mm(a, b) and addmm(bias, a, b): the left operand is second to last
+            if not isinstance(left, TensorSpec) or len(left.shape) != 2:
+                return TENSOR_CORE_MIN_FLOPS         # malformed; _make_gemm reports it
+            return 2 * prod(op.output.shape) * left.shape[1]
+
         products = [op for op in self.ops if op.op in ("mm", "addmm")]
-        self.tiny_products = bool(products) and all(2 * prod(op.output.shape) * (op.inputs[-2].shape[1] if isinstance(op.inputs[-2], TensorSpec) and len(op.inputs[-2].shape) == 2 else 1 << 30) < TENSOR_CORE_MIN_FLOPS for op in products)
+        self.tiny_products = bool(products) and all(product_flops(op) < TENSOR_CORE_MIN_FLOPS for op in products)
         self.index = {op.output.buffer: i for i, op in enumerate(self.ops)}
         self.producer = {op.output.buffer: op for op in self.ops}
         self.input_index = {spec.buffer: i for i, spec in enumerate(program.inputs)}
