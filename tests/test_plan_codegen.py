@@ -376,3 +376,26 @@ def test_simt_gemms_stage_no_deeper_than_their_k():
     assert set(re.findall(r"tk::gemm_simt<(\d+),", forced.source)) == {"128"}
     with pytest.raises(ValueError, match="simt_depth"):
         generate(program, simt_depth=48)
+
+
+def test_aligned_row_accesses_are_emitted_only_where_the_layout_proves_them():
+    work = workloads.mlp_workload("tiny", (128, 256, 128), 16)
+    x, target = work.batches[0]
+    inplace = {5 + i: i for i in range(4)}
+    program, _ = tk.capture(work.fn(), (work.state, x, target))
+    g = generate(program, inplace_outputs=inplace)
+    # W1, b1, W2, b2 (read by the dW / bias epilogues and written in place) and the target lean on aligned pointers;
+    # x is only ever a TMA operand, whose alignment the tensor-map encoder checks
+    assert g.aligned_inputs == (0, 1, 2, 3, 5) and g.aligned_workspace and g.aligned_outputs
+    assert "tk::ld_row_full<" in g.source and "tk::st_row_full<" in g.source
+    # the same step on a target whose rows are 132 elements apart (264 bytes: every other row starts off a 16-byte
+    # boundary): its loads keep the element-wise fallback and its pointer is not constrained; the rest is unchanged.
+    # (A slice that merely STARTS at an odd offset has a provable layout and an unaligned pointer: the launch refuses it.)
+    sliced = torch.empty(16, 132, dtype=target.dtype)[:, :128]
+    viewed, _ = tk.capture(work.fn(), (work.state, x, sliced))
+    v = generate(viewed, inplace_outputs=inplace)
+    assert v.aligned_inputs == (0, 1, 2, 3) and v.aligned_outputs == g.aligned_outputs
+    assert v.source.count("tk::ld_row_full<") == g.source.count("tk::ld_row_full<") - 1
+    # switched off, nothing is assumed and nothing is required
+    off = generate(program, inplace_outputs=inplace, assume_aligned=False)
+    assert not off.aligned_inputs and not off.aligned_outputs and not off.aligned_workspace and "_full<" not in off.source
