@@ -105,8 +105,43 @@ def sharded_stage_profile(sizes, batch: int, *, repeats: int = 5, seed: int = 0,
     return records
 
 
+def launch_span_profile(fn: Callable[..., Any], example_inputs: Sequence[Any], batches: Sequence[Any], *, graph_steps: int = 20,
+                        replays: int = 10, **options: Any) -> dict:
+    """Where a captured step spends its time OUTSIDE the stages: a stamped kernel in a `graph_steps`-step CUDA
+    graph, replayed `replays` times under CUDA events.  Microseconds, medians: `period` per step of the replay,
+    `prologue` / `stages` / `tail` / `total` of the graph's last launch (`CompiledProgram.launch_span`), and
+    `gap_between_launches` = period - total, what the launch itself costs between two dependent kernels."""
+    import statistics
+    state = example_inputs[0]
+    compiled = compile_training(fn, example_inputs, stage_stamps=True, **options)
+    for i in range(3):
+        compiled(state, *batches[i % len(batches)])
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(graph_steps):
+            compiled(state, *batches[i % len(batches)])
+    graph.replay()
+    torch.cuda.synchronize()
+    periods, spans = [], []
+    for _ in range(replays):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        graph.replay()
+        end.record()
+        end.synchronize()
+        periods.append(begin.elapsed_time(end) * 1e3 / graph_steps)
+        spans.append(compiled.runner.launch_span())
+    compiled.runner.status()
+    record = {key: statistics.median(span[key] for span in spans) / 1e3 for key in spans[0]}
+    record["period"] = statistics.median(periods)
+    record["gap_between_launches"] = record["period"] - record["total"]
+    return {key: round(value, 2) for key, value in record.items()}
+
+
 def main(argv=None) -> int:
-    """`python -m trainkernel_b200.profile c4` prints the stage table of a named workload as JSON lines.
+    """`python -m trainkernel_b200.profile c4` prints the stage table of a named workload as JSON lines;
+    `--span` prints what a captured step costs outside its stages instead.
 
     `--plain` compiles without stamps and only launches the step `--repeats` times: the command to
     put under a hardware profiler.
@@ -124,6 +159,8 @@ def main(argv=None) -> int:
     parser.add_argument("--no-multicast", action="store_true")
     parser.add_argument("--repeats", type=int, default=10)
     parser.add_argument("--plain", action="store_true")
+    parser.add_argument("--span", action="store_true",
+                        help="prologue, stages, tail and launch gap of the step inside a 20-step CUDA graph")
     parser.add_argument("--device", default="cuda:0")
     parser.add_argument("--trace-stage", type=int, default=None,
                         help="also time the roles of the first single-CTA tensor-core tile of this stage")
@@ -153,6 +190,9 @@ def main(argv=None) -> int:
         return 0
     work = workloads.build(args.workload, device=args.device)
     inputs = (work.state, *work.batches[0])
+    if args.span:
+        print(json.dumps({"workload": work.name, "us": launch_span_profile(work.fn(), inputs, work.batches, replays=args.repeats)}))
+        return 0
     if args.plain:
         compiled = compile_training(work.fn(), inputs)
         for _ in range(args.repeats):
